@@ -37,6 +37,11 @@ class KvNeed:
     n_kv_heads: int
     head_dim: int
     window: int = 0                     # 0: all keys; w: the last w
+    v_head_dim: int = 0                 # the values' head size; 0: the keys'
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_head_dim or self.head_dim
 
 
 @dataclass(frozen=True)
@@ -51,7 +56,7 @@ class StateNeed:
 class CacheView:
     """What a mixer gets for one cache entry."""
     k: torch.Tensor                     # [pages, kv_heads, page_tokens, head_dim]
-    v: torch.Tensor
+    v: torch.Tensor                     # the same with the values' head size
     page_table: torch.Tensor            # [slots, max_pages] int32, device
     page_tokens: int
     need: KvNeed
@@ -70,7 +75,7 @@ class KvGroup:
         # Zeroed once here; a page that has been used is zeroed again (values only: scores of keys past
         # the end are replaced, not multiplied) when it is handed on to a step that leaves rows unwritten.
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = torch.zeros((*shape[:-1], need.value_dim), dtype=dtype, device=device)
         self._used = np.zeros(n_pages, dtype=bool)
         self._to_zero: list[int] = []
         self.table_host = np.full((n_slots, max_pages), -1, dtype=np.int32)
@@ -98,7 +103,7 @@ class KvGroup:
 
     @property
     def bytes(self) -> int:
-        return 2 * self.k.numel() * self.k.element_size()
+        return (self.k.numel() + self.v.numel()) * self.k.element_size()
 
     def pages_needed(self, slot: int, new_length: int) -> int:
         return max(0, -(-new_length // self.page_tokens) - self.first_page[slot] - self.held[slot])
@@ -173,24 +178,44 @@ class KvGroup:
 
 
 class StateStore:
-    """Per-sequence state of fixed size: for each name a tensor [slots, *shape].
-    It is there for mixers that carry state from token to token; a model whose
-    mixers need none has an empty store."""
+    """Per-sequence state of fixed size: for each key a tensor [slots, *shape], or, where a part asks for
+    several (a mapping name -> StateNeed), a dict of such tensors.  It is there for parts that carry state
+    from token to token; a model whose parts need none has an empty store.  All tensors of one type lie in
+    one buffer [slots, words], so that taking a slot clears its state with one call per type."""
 
-    def __init__(self, needs: Mapping[object, StateNeed], n_slots: int, device):
-        self.tensors = {key: torch.zeros((n_slots, *need.shape), dtype=need.dtype, device=device)
-                        for key, need in needs.items()}
+    def __init__(self, needs: Mapping[object, object], n_slots: int, device):
+        flat = []                                   # (key, name or None, need)
+        for key, need in needs.items():
+            if isinstance(need, Mapping):
+                flat += [(key, name, n) for name, n in need.items()]
+            else:
+                flat.append((key, None, need))
+        self._buffers = {}
+        self.tensors = {}
+        for dtype in dict.fromkeys(n.dtype for _, _, n in flat):
+            mine = [(k, name, n) for k, name, n in flat if n.dtype == dtype]
+            sizes = [int(np.prod(n.shape, dtype=np.int64)) for _, _, n in mine]
+            buf = self._buffers[dtype] = torch.zeros((n_slots, sum(sizes)), dtype=dtype, device=device)
+            at = 0
+            for (key, name, need), size in zip(mine, sizes):
+                t = buf[:, at:at + size].view(n_slots, *need.shape)
+                at += size
+                if name is None:
+                    self.tensors[key] = t
+                else:
+                    self.tensors.setdefault(key, {})[name] = t
 
     def reset(self, slot: int) -> None:
-        for t in self.tensors.values():
-            t[slot].zero_()
+        for buf in self._buffers.values():
+            buf[slot].zero_()
 
-    def get(self, key):
-        return self.tensors.get(key)
+    def get(self, key, name=None):
+        t = self.tensors.get(key)
+        return t if name is None or t is None else t[name]
 
     @property
     def bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in self.tensors.values())
+        return sum(t.numel() * t.element_size() for t in self._buffers.values())
 
 
 class SequenceCache:

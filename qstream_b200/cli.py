@@ -99,7 +99,7 @@ def main(argv=None) -> int:
         max_batch = max(1, min(args.max_batch, len(prompts)))
         max_tokens = max_batch * (-(-min(ctx, model.spec.max_positions) // 64) * 64)
         if args.ram_budget:
-            per_token = sum(2 * n.n_kv_heads * n.head_dim for n in model.kv_needs().values()) * \
+            per_token = sum(n.n_kv_heads * (n.head_dim + n.value_dim) for n in model.kv_needs().values()) * \
                 torch.empty((), dtype=model.runtime.dtype).element_size()
             max_tokens = min(max_tokens, max(64, args.ram_budget * 2**20 // max(per_token, 1) // 64 * 64))
         engine = qs.Engine(model, qs.EngineConfig(max_tokens=max_tokens, max_batch=max_batch, max_context=ctx,

@@ -2,7 +2,7 @@
 
 QStream's converter keeps a dict `model_type -> arch` and falls back to llama for
 unknown types (tools/convert_hf.py:1540-1569).  Here `architectures[0]` of
-config.json (or `model_type`, as an alias) is looked up; an unknown name is an
+config.json (or `architecture`, or `model_type` as an alias) is looked up; an unknown name is an
 error, never a silent fallback.
 
 A configuration class offers `from_dict(dict)`, `to_dict()`, `model_spec()` and the
@@ -41,10 +41,12 @@ def config_class_for(name: str):
 
 def config_from_dict(d: dict):
     archs = d.get("architectures") or []
-    name = archs[0] if archs else d.get("model_type")
-    if not name:
+    if isinstance(archs, str):
+        archs = [archs]
+    name = archs[0] if archs else (d.get("architecture") or d.get("model_type"))
+    if not name or not isinstance(name, str):
         raise QStreamError(QsError.INVALID_MODEL,
-                           "config.json names no architecture ('architectures' or 'model_type')")
+                           "config.json names no architecture ('architectures', 'architecture' or 'model_type')")
     return config_class_for(name).from_dict(d)
 
 

@@ -1,7 +1,8 @@
 // Rotary position encoding fused with the write of keys and values into the paged
 // cache, and causal attention of each token over its sequence's cache.
 //
-// Cache entry layout: K and V each [n_pages][n_kv_heads][page_tokens][head_dim].
+// Cache entry layout: K [n_pages][n_kv_heads][page_tokens][head_dim], V the same with the values' head size
+// (dv, which may differ from the keys').
 // A sequence (slot) owns a row of `page_table` ([n_slots][max_pages], int32); position
 // p of the sequence lies in page page_table[slot][p / page_tokens] at row
 // p % page_tokens.  A token with slot < 0 is padding: nothing is read or written for it.
@@ -24,7 +25,8 @@ __global__ void rope_store_kernel(T* __restrict__ q, const T* __restrict__ k, co
                                   const int32_t* __restrict__ tok_slot, const int32_t* __restrict__ tok_pos,
                                   const int32_t* __restrict__ page_table, int max_pages, int page_shift,
                                   T* __restrict__ k_cache, T* __restrict__ v_cache,
-                                  int32_t* __restrict__ status) {
+                                  int32_t* __restrict__ status, int dv, const T* __restrict__ v_first, size_t ldvf,
+                                  float lam) {
     // blockIdx.x = token; the gridDim.y blocks of a token share its (head, pair of dims) items of q, then k and v
     grid_dep_launch();
     grid_dep_wait();
@@ -53,10 +55,10 @@ __global__ void rope_store_kernel(T* __restrict__ q, const T* __restrict__ k, co
     if (n_kv_heads == 0) return;
     const int page = page_table[(size_t)slot * max_pages + (pos >> page_shift)];
     if (page < 0) { if (threadIdx.x == 0) atomicExch(status, 2); return; }
-    const size_t in_page = (size_t)(pos & (page_tokens - 1)) * dh;
+    const size_t in_page = (size_t)(pos & (page_tokens - 1));
     for (int e = tid; e < n_kv_heads * half; e += stride) {
         const int kvh = e / half, j = e - kvh * half;
-        const size_t dst_off = ((size_t)page * n_kv_heads + kvh) * page_tokens * dh + in_page;
+        const size_t dst_off = (((size_t)page * n_kv_heads + kvh) * page_tokens + in_page) * dh;
         const T* krow = k + (size_t)t * ldk + (size_t)kvh * dh;
         T* kdst = k_cache + dst_off;
         if (rotate && 2 * j < R) {
@@ -68,10 +70,15 @@ __global__ void rope_store_kernel(T* __restrict__ q, const T* __restrict__ k, co
             kdst[2 * j] = krow[2 * j];
             kdst[2 * j + 1] = krow[2 * j + 1];
         }
-        const T* vrow = v + (size_t)t * ldv + (size_t)kvh * dh;
-        T* vdst = v_cache + dst_off;
-        vdst[2 * j] = vrow[2 * j];
-        vdst[2 * j + 1] = vrow[2 * j + 1];
+    }
+    // values: kept as they are, or blended with another layer's values of the same token,
+    // (1 - lam) v + lam v_first, in 32-bit and rounded once
+    for (int e = tid; e < n_kv_heads * dv; e += stride) {
+        const int kvh = e / dv, j = e - kvh * dv;
+        const size_t dst_off = (((size_t)page * n_kv_heads + kvh) * page_tokens + in_page) * dv;
+        const T val = v[(size_t)t * ldv + (size_t)kvh * dv + j];
+        v_cache[dst_off + j] = v_first ? from_f32<T>((1.0f - lam) * to_f32(val) + lam * to_f32(v_first[(size_t)t * ldvf + (size_t)kvh * dv + j]))
+                                       : val;
     }
 }
 
@@ -99,7 +106,8 @@ __global__ void rope_store_vec_kernel(__nv_bfloat16* __restrict__ q, const __nv_
                                       const int32_t* __restrict__ tok_slot, const int32_t* __restrict__ tok_pos,
                                       const int32_t* __restrict__ page_table, int max_pages, int page_shift,
                                       __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
-                                      int32_t* __restrict__ status, int settled) {
+                                      int32_t* __restrict__ status, int settled, int dv,
+                                      const __nv_bfloat16* __restrict__ v_first, size_t ldvf, float lam) {
     grid_dep_launch();
     // `settled`: the step's slots, positions and pages and the table of angles were complete before the
     // previous kernel of the stream began.  Then they are fetched (the table's row only as far as L2) while
@@ -131,14 +139,33 @@ __global__ void rope_store_vec_kernel(__nv_bfloat16* __restrict__ q, const __nv_
     }
     if (n_kv_heads == 0) return;
     if (page < 0) { if (threadIdx.x == 0) atomicExch(status, 2); return; }
-    const size_t in_page = (size_t)(pos & (page_tokens - 1)) * dh;
-    for (int e = tid; e < n_kv_heads * hc; e += stride) {
-        const int kvh = e / hc, c = e - kvh * hc;
-        const size_t dst = ((size_t)page * n_kv_heads + kvh) * page_tokens * dh + in_page + c * 8;
-        uint4 kk = *reinterpret_cast<const uint4*>(k + (size_t)t * ldk + (size_t)kvh * dh + c * 8);
-        if (rotate && c < rc) kk = rotate8(kk, cs + c * 8);
-        *reinterpret_cast<uint4*>(k_cache + dst) = kk;
-        *reinterpret_cast<uint4*>(v_cache + dst) = *reinterpret_cast<const uint4*>(v + (size_t)t * ldv + (size_t)kvh * dh + c * 8);
+    const size_t in_page = (size_t)(pos & (page_tokens - 1));
+    const int vc = dv >> 3;                                              // 16-byte chunks of a head's values
+    for (int e = tid; e < n_kv_heads * (hc + vc); e += stride) {
+        const int kvh = e / (hc + vc), c = e - kvh * (hc + vc);
+        const size_t row = ((size_t)page * n_kv_heads + kvh) * page_tokens + in_page;
+        if (c < hc) {
+            uint4 kk = *reinterpret_cast<const uint4*>(k + (size_t)t * ldk + (size_t)kvh * dh + c * 8);
+            if (rotate && c < rc) kk = rotate8(kk, cs + c * 8);
+            *reinterpret_cast<uint4*>(k_cache + row * dh + c * 8) = kk;
+        } else {
+            const int cv = c - hc;
+            uint4 vv = *reinterpret_cast<const uint4*>(v + (size_t)t * ldv + (size_t)kvh * dv + cv * 8);
+            if (v_first) {              // (1 - lam) v + lam v_first in 32-bit, rounded once
+                const uint4 ff = *reinterpret_cast<const uint4*>(v_first + (size_t)t * ldvf + (size_t)kvh * dv + cv * 8);
+                const uint32_t a[4] = {vv.x, vv.y, vv.z, vv.w}, b[4] = {ff.x, ff.y, ff.z, ff.w};
+                uint32_t o[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float x0 = __uint_as_float(a[i] << 16), x1 = __uint_as_float(a[i] & 0xffff0000u);
+                    const float y0 = __uint_as_float(b[i] << 16), y1 = __uint_as_float(b[i] & 0xffff0000u);
+                    const __nv_bfloat162 r = __floats2bfloat162_rn((1.0f - lam) * x0 + lam * y0, (1.0f - lam) * x1 + lam * y1);
+                    o[i] = *reinterpret_cast<const uint32_t*>(&r);
+                }
+                vv = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+            *reinterpret_cast<uint4*>(v_cache + row * dv + cv * 8) = vv;
+        }
     }
 }
 
@@ -151,7 +178,8 @@ __global__ void rope_store_vec_kernel(__nv_bfloat16* __restrict__ q, const __nv_
 // added in key order (src/engine.c:913-922).  Scores, maximum, exponentials, sum and
 // the output accumulator are 32-bit.  The order of the sums depends only on the
 // token's own position, never on the batch or on where the pages lie.
-// Lane l owns output dims l, l+32, ...: NACC = ceil(dh / 32) accumulators.
+// Lane l owns output dims l, l+32, ...: NACC = ceil(dv / 32) accumulators (dv: the values' head size).
+// softcap > 0: s <- softcap * tanh(s / softcap) before the softmax.
 template <typename T, int NACC>
 __global__ void __launch_bounds__(128)
 attention_kernel(T* __restrict__ out, const T* __restrict__ q, size_t ldo, size_t ldq,
@@ -159,17 +187,17 @@ attention_kernel(T* __restrict__ out, const T* __restrict__ q, size_t ldo, size_
                  const int32_t* __restrict__ page_table, int max_pages, int page_shift,
                  const int32_t* __restrict__ tok_slot, const int32_t* __restrict__ tok_pos,
                  int T_tokens, int n_heads, int n_kv_heads, int dh, float scale, int window,
-                 int32_t* __restrict__ status) {
+                 int32_t* __restrict__ status, int dv, float softcap) {
     extern __shared__ float q_smem[];               // [warps][dh]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int warps = blockDim.x >> 5;
     const long long item = (long long)blockIdx.x * warps + warp;
     if (item >= (long long)T_tokens * n_heads) return;
     const int t = (int)(item / n_heads), head = (int)(item % n_heads);
-    T* o = out + (size_t)t * ldo + (size_t)head * dh;
+    T* o = out + (size_t)t * ldo + (size_t)head * dv;
     const int slot = tok_slot[t];
     if (slot < 0) {                                 // padding: defined output, no cache access
-        for (int d = lane; d < dh; d += 32) o[d] = from_f32<T>(0.f);
+        for (int d = lane; d < dv; d += 32) o[d] = from_f32<T>(0.f);
         return;
     }
     const int pos = tok_pos[t];
@@ -197,12 +225,13 @@ attention_kernel(T* __restrict__ out, const T* __restrict__ q, size_t ldo, size_
             const int page = pages[key >> page_shift];
             if (page < 0) { atomicExch(status, 3); }
             else {
-                const size_t off = (((size_t)page * n_kv_heads + kvh) * page_tokens + (key & (page_tokens - 1))) * dh;
-                const T* krow = k_cache + off;
-                vrow = v_cache + off;
+                const size_t off = ((size_t)page * n_kv_heads + kvh) * page_tokens + (key & (page_tokens - 1));
+                const T* krow = k_cache + off * dh;
+                vrow = v_cache + off * dv;
                 float dot = 0.f;
                 for (int d = 0; d < dh; ++d) dot = fmaf(qs[d], to_f32(krow[d]), dot);
                 s = dot * scale;
+                if (softcap > 0.f) s = softcap * tanhf(s / softcap);
             }
         }
         const float m_new = fmaxf(m, warp_max(s));
@@ -219,7 +248,7 @@ attention_kernel(T* __restrict__ out, const T* __restrict__ q, size_t ldo, size_
 #pragma unroll
             for (int i = 0; i < NACC; ++i) {
                 const int d = lane + 32 * i;
-                if (d < dh) acc[i] = fmaf(pj, to_f32(vj[d]), acc[i]);
+                if (d < dv) acc[i] = fmaf(pj, to_f32(vj[d]), acc[i]);
             }
         }
         m = m_new;
@@ -228,7 +257,7 @@ attention_kernel(T* __restrict__ out, const T* __restrict__ q, size_t ldo, size_
 #pragma unroll
     for (int i = 0; i < NACC; ++i) {
         const int d = lane + 32 * i;
-        if (d < dh) o[d] = from_f32<T>(acc[i] * inv);
+        if (d < dv) o[d] = from_f32<T>(acc[i] * inv);
     }
 }
 
@@ -236,7 +265,7 @@ template <typename T>
 int launch_attention(void* out, const void* q, long long ldo, long long ldq, const void* k_cache,
                      const void* v_cache, const int32_t* page_table, int max_pages, int page_shift,
                      const int32_t* tok_slot, const int32_t* tok_pos, int T_tokens, int n_heads,
-                     int n_kv_heads, int dh, float scale, int window, int32_t* status,
+                     int n_kv_heads, int dh, float scale, int window, int32_t* status, int dv, float softcap,
                      cudaStream_t stream) {
     const int warps = 4;
     const long long items = (long long)T_tokens * n_heads;
@@ -245,8 +274,8 @@ int launch_attention(void* out, const void* q, long long ldo, long long ldq, con
 #define GO(NACC) attention_kernel<T, NACC><<<blocks, warps * 32, smem, stream>>>( \
         (T*)out, (const T*)q, (size_t)ldo, (size_t)ldq, (const T*)k_cache, (const T*)v_cache, \
         page_table, max_pages, page_shift, tok_slot, tok_pos, T_tokens, n_heads, n_kv_heads, dh, \
-        scale, window, status)
-    const int nacc = (dh + 31) / 32;
+        scale, window, status, dv, softcap)
+    const int nacc = (dv + 31) / 32;
     if (nacc <= 1) GO(1);
     else if (nacc <= 2) GO(2);
     else if (nacc <= 4) GO(4);
@@ -267,8 +296,9 @@ QS_API int qs_rope_store(void* q, const void* k, const void* v, int dtype,
                          const int32_t* tok_slot, const int32_t* tok_pos,
                          const int32_t* page_table, int max_pages, int page_tokens,
                          void* k_cache, void* v_cache, int T_tokens, int32_t* status,
-                         int settled, cudaStream_t stream) {
+                         int settled, int dv, const void* v_first, long long ldvf, float lam, cudaStream_t stream) {
     if (T_tokens == 0) return QS_OK;
+    if (dv <= 0) dv = dh;
     QS_REQUIRE(T_tokens > 0 && n_heads >= 0 && n_kv_heads >= 0 && n_heads + n_kv_heads > 0 && dh > 0, "rope_store: bad sizes");
     QS_REQUIRE(n_kv_heads == 0 || (k && v && k_cache && v_cache), "rope_store: keys and values without a cache to keep them");
     QS_REQUIRE(dh % 2 == 0, "rope_store: head size %d must be even", dh);
@@ -281,29 +311,31 @@ QS_API int qs_rope_store(void* q, const void* k, const void* v, int dtype,
     int per_token = 1;                       // few tokens (decode): several blocks per token
     if (T_tokens < 256) { per_token = (n_kv_heads * dh / 2 + threads - 1) / threads; if (per_token > 16) per_token = 16; if (per_token < 1) per_token = 1; }
     dim3 grid(T_tokens, per_token);
-    const bool aligned = dh % 8 == 0 && R % 8 == 0 && ldq % 8 == 0 && ldk % 8 == 0 && ldv % 8 == 0 &&
+    const bool aligned = dh % 8 == 0 && dv % 8 == 0 && R % 8 == 0 && ldq % 8 == 0 && ldk % 8 == 0 && ldv % 8 == 0 &&
+                         ldvf % 8 == 0 && ((uintptr_t)v_first % 16) == 0 &&
                          ((uintptr_t)q % 16) == 0 && ((uintptr_t)k % 16) == 0 && ((uintptr_t)v % 16) == 0 &&
                          ((uintptr_t)k_cache % 16) == 0 && ((uintptr_t)v_cache % 16) == 0 && ((uintptr_t)cos_sin % 16) == 0;
     if (dtype == QS_BF16 && aligned) {
-        const int work8 = (n_heads * (R / 8) + n_kv_heads * (dh / 8));
+        const int work8 = (n_heads * (R / 8) + n_kv_heads * ((dh + dv) / 16));
         const int threads8 = work8 >= 512 ? 128 : 64;
         int per = 1;
-        if (T_tokens < 256) { per = (n_kv_heads * (dh / 8) + threads8 - 1) / threads8; if (per > 16) per = 16; if (per < 1) per = 1; }
+        if (T_tokens < 256) { per = (n_kv_heads * ((dh + dv) / 16) + threads8 - 1) / threads8; if (per > 16) per = 16; if (per < 1) per = 1; }
         cudaError_t e = qs_launch_dependent(rope_store_vec_kernel, dim3(T_tokens, per), dim3(threads8), 0, stream,
             (__nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (size_t)ldq, (size_t)ldk, (size_t)ldv,
             n_heads, n_kv_heads, dh, R, cos_sin, max_pos, tok_slot, tok_pos, page_table, max_pages, shift,
-            (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, status, settled);
+            (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, status, settled, dv, (const __nv_bfloat16*)v_first, (size_t)ldvf, lam);
         if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "rope_store: %s", cudaGetErrorString(e));
         return qs_check_launch("rope_store");
     }
     if (dtype == QS_F32)
         qs_launch_dependent(rope_store_kernel<float>, grid, dim3(threads), 0, stream, (float*)q, (const float*)k, (const float*)v,
             (size_t)ldq, (size_t)ldk, (size_t)ldv, n_heads, n_kv_heads, dh, R, cos_sin, max_pos, tok_slot, tok_pos,
-            page_table, max_pages, shift, (float*)k_cache, (float*)v_cache, status);
+            page_table, max_pages, shift, (float*)k_cache, (float*)v_cache, status, dv, (const float*)v_first, (size_t)ldvf, lam);
     else if (dtype == QS_BF16)
         qs_launch_dependent(rope_store_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, (__nv_bfloat16*)q, (const __nv_bfloat16*)k,
             (const __nv_bfloat16*)v, (size_t)ldq, (size_t)ldk, (size_t)ldv, n_heads, n_kv_heads, dh, R, cos_sin, max_pos,
-            tok_slot, tok_pos, page_table, max_pages, shift, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, status);
+            tok_slot, tok_pos, page_table, max_pages, shift, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, status, dv,
+            (const __nv_bfloat16*)v_first, (size_t)ldvf, lam);
     else return qs_fail(QS_ERR_INVALID_INPUT, "rope_store: unknown dtype %d", dtype);
     return qs_check_launch("rope_store");
 }
@@ -313,8 +345,10 @@ QS_API int qs_attention(void* out, const void* q, int dtype, long long ldo, long
                         const int32_t* page_table, int max_pages, int page_tokens,
                         const int32_t* tok_slot, const int32_t* tok_pos, int T_tokens,
                         int n_heads, int n_kv_heads, int dh, float scale, int window,
-                        int32_t* status, cudaStream_t stream) {
+                        int32_t* status, int dv, float softcap, cudaStream_t stream) {
     if (T_tokens == 0) return QS_OK;
+    if (dv <= 0) dv = dh;
+    QS_REQUIRE(dv <= 512, "attention: value head size %d above 512", dv);
     QS_REQUIRE(T_tokens > 0 && n_heads > 0 && n_kv_heads > 0 && dh > 0, "attention: bad sizes");
     QS_REQUIRE(n_heads % n_kv_heads == 0, "attention: %d query heads are no multiple of %d key heads", n_heads, n_kv_heads);
     QS_REQUIRE(dh <= 512, "attention: head size %d above 512", dh);
@@ -324,10 +358,10 @@ QS_API int qs_attention(void* out, const void* q, int dtype, long long ldo, long
     while ((1 << shift) < page_tokens) ++shift;
     if (dtype == QS_F32)
         return launch_attention<float>(out, q, ldo, ldq, k_cache, v_cache, page_table, max_pages, shift, tok_slot,
-                                       tok_pos, T_tokens, n_heads, n_kv_heads, dh, scale, window, status, stream);
+                                       tok_pos, T_tokens, n_heads, n_kv_heads, dh, scale, window, status, dv, softcap, stream);
     if (dtype == QS_BF16)
         return launch_attention<__nv_bfloat16>(out, q, ldo, ldq, k_cache, v_cache, page_table, max_pages, shift,
                                                tok_slot, tok_pos, T_tokens, n_heads, n_kv_heads, dh, scale, window,
-                                               status, stream);
+                                               status, dv, softcap, stream);
     return qs_fail(QS_ERR_INVALID_INPUT, "attention: unknown dtype %d", dtype);
 }

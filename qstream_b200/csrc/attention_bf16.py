@@ -80,6 +80,8 @@ def prefill(q, n_heads, n_kv_heads, head_dim, scale, window, tiles, page_table, 
 def attend(q, spec, step, view, out=None):
     """The specialised kernel's output, or None if the generic kernel is to run."""
     b = step.batch
+    if spec.value_dim != spec.head_dim or spec.softcap:
+        return None
     if (b.decode and view.page_tokens == 64 and spec.head_dim % 8 == 0 and spec.head_dim <= 512
             and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0):
         # the grid covers the longest sequence of the step (a captured step: the bound it was captured for),

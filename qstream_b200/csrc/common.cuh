@@ -15,7 +15,8 @@
 
 enum QsDtype { QS_F32 = 0, QS_BF16 = 1 };
 
-enum QsActivation { QS_ACT_NONE = 0, QS_ACT_GELU_TANH = 1, QS_ACT_GELU_ERF = 2 };
+enum QsActivation { QS_ACT_NONE = 0, QS_ACT_GELU_TANH = 1, QS_ACT_GELU_ERF = 2, QS_ACT_SILU = 3, QS_ACT_SIGMOID = 4,
+                    QS_ACT_TANH = 5 };
 
 // Codes follow QsError in errors.py (QStream include/qsf/error.h:14-32).
 enum { QS_OK = 0, QS_ERR_INVALID_INPUT = 11, QS_ERR_INTERNAL = 15 };
@@ -137,14 +138,24 @@ __device__ __forceinline__ float gelu_erf(float v) {
     return 0.5f * v * (1.0f + erff(v * 0.7071067811865476f));
 }
 
+// sigmoid(v) = 1 / (1 + exp(-v)) and silu(v) = v sigmoid(v), in 32-bit with the full-precision exponential.
+__device__ __forceinline__ float sigmoid_f32(float v) { return 1.0f / (1.0f + expf(-v)); }
+__device__ __forceinline__ float silu_f32(float v) { return v / (1.0f + expf(-v)); }
+
 __device__ __forceinline__ float apply_activation(float v, int act) {
     if (act == QS_ACT_GELU_TANH) return gelu_tanh(v);
     if (act == QS_ACT_GELU_ERF) return gelu_erf(v);
+    if (act == QS_ACT_SILU) return silu_f32(v);
+    if (act == QS_ACT_SIGMOID) return sigmoid_f32(v);
+    if (act == QS_ACT_TANH) return tanhf(v);
     return v;
 }
 
 __device__ __forceinline__ float apply_activation_fast(float v, int act) {
     if (act == QS_ACT_GELU_TANH) return gelu_tanh_fast(v);
     if (act == QS_ACT_GELU_ERF) return gelu_erf(v);
+    if (act == QS_ACT_SILU) return __fdividef(v, 1.0f + __expf(-v));
+    if (act == QS_ACT_SIGMOID) return __fdividef(1.0f, 1.0f + __expf(-v));
+    if (act == QS_ACT_TANH) return 1.0f - __fdividef(2.0f, __expf(2.0f * v) + 1.0f);
     return v;
 }

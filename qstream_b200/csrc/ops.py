@@ -16,8 +16,9 @@ from ..errors import QsError, QStreamError
 from . import build as _build
 
 F32, BF16 = 0, 1
-ACT_NONE, ACT_GELU_TANH, ACT_GELU_ERF = 0, 1, 2
-ACTIVATIONS = {None: ACT_NONE, "none": ACT_NONE, "gelu_new": ACT_GELU_TANH, "gelu": ACT_GELU_ERF}
+ACT_NONE, ACT_GELU_TANH, ACT_GELU_ERF, ACT_SILU, ACT_SIGMOID, ACT_TANH = 0, 1, 2, 3, 4, 5
+ACTIVATIONS = {None: ACT_NONE, "none": ACT_NONE, "gelu_new": ACT_GELU_TANH, "gelu": ACT_GELU_ERF,
+               "silu": ACT_SILU, "sigmoid": ACT_SIGMOID, "tanh": ACT_TANH}
 
 _lib = None
 
@@ -32,10 +33,23 @@ _SIGNATURES = {
                         c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p], c_int),
     "qs_rope_store": ([c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_longlong,
                        c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                       c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p], c_int),
+                       c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_longlong, c_float, c_void_p], c_int),
     "qs_attention": ([c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
                       c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
-                      c_void_p], c_int),
+                      c_int, c_float, c_void_p], c_int),
+    "qs_residual_rmsnorm": ([c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int,
+                             c_longlong, c_float, c_void_p, c_int, c_float, c_int, c_int, c_float, c_void_p], c_int),
+    "qs_gated_group_norm": ([c_void_p, c_int, c_longlong, c_void_p, c_int, c_longlong, c_void_p, c_int, c_void_p, c_int,
+                             c_longlong, c_int, c_int, c_int, c_int, c_float, c_void_p], c_int),
+    "qs_gated_act": ([c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p], c_int),
+    "qs_embedding_hashed": ([c_void_p, c_int, c_void_p, c_void_p, c_int, c_float, c_longlong, c_longlong, c_longlong,
+                             c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p], c_int),
+    "qs_keep_last_rows": ([c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_int, c_void_p], c_int),
+    "qs_state_scan": ([c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int,
+                       c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int,
+                       c_int, c_int, c_int, c_int, c_int, c_void_p], c_int),
+    "qs_token_shift": ([c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_longlong,
+                        c_void_p, c_void_p, c_int, c_int, c_int, c_void_p], c_int),
     "qs_argmax": ([c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p], c_int),
     "qs_repeat_penalty": ([c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_void_p, c_float, c_void_p], c_int),
     "qs_sample": ([c_void_p, c_void_p, c_int, c_int, c_longlong, c_float, c_int, c_float, c_void_p, c_void_p], c_int),
@@ -220,9 +234,12 @@ def linear_simt(x, weight, bias=None, activation=None, residuals=(), out_dtype=N
 
 
 def rope_store(q, k, v, n_heads, n_kv_heads, head_dim, rotary_dim, cos_sin, tok_slot, tok_pos,
-               page_table, page_tokens, k_cache, v_cache, status, settled=False) -> None:
+               page_table, page_tokens, k_cache, v_cache, status, settled=False, v_head_dim=None,
+               v_first=None, v_mix=0.0) -> None:
     """Rotate q (in place) and k, and write k and v into the paged cache entry.
     k = v = None (n_kv_heads = 0): rotate q only (no page table is needed then).
+    `v_head_dim`: the values' head size where it differs from the keys'.  `v_first` (same shape as v):
+    the cache keeps (1 - v_mix) v + v_mix v_first instead of v.
     `settled`: slots, positions, page table and the table of angles were complete before the previous kernel
     of the stream began (a step's own are); the kernel then reads them early."""
     ref = k if k is not None else q
@@ -235,20 +252,135 @@ def rope_store(q, k, v, n_heads, n_kv_heads, head_dim, rotary_dim, cos_sin, tok_
         ptr(cos_sin), max_pos, _int32(tok_slot, "tok_slot"), _int32(tok_pos, "tok_pos"),
         _int32(page_table, "page_table") if page_table is not None else None,
         page_table.shape[1] if page_table is not None else 0, page_tokens, ptr(k_cache), ptr(v_cache), T,
-        ptr(status), int(bool(settled)), stream()))
+        ptr(status), int(bool(settled)), int(v_head_dim or head_dim), ptr(v_first),
+        v_first.stride(0) if v_first is not None else 0, float(v_mix), stream()))
 
 
 def attention(q, n_heads, n_kv_heads, head_dim, scale, window, tok_slot, tok_pos, page_table,
-              page_tokens, k_cache, v_cache, status, out=None) -> torch.Tensor:
-    """Causal attention of every token over its sequence's cache (generic kernel)."""
+              page_tokens, k_cache, v_cache, status, out=None, v_head_dim=None, softcap=0.0) -> torch.Tensor:
+    """Causal attention of every token over its sequence's cache (generic kernel).  `v_head_dim`: the values'
+    head size where it differs from the keys'; `softcap` c > 0: scores become c tanh(s / c) before the softmax."""
     T = q.shape[0]
+    dv = int(v_head_dim or head_dim)
     if out is None:
-        out = torch.empty((T, n_heads * head_dim), dtype=q.dtype, device=q.device)
+        out = torch.empty((T, n_heads * dv), dtype=q.dtype, device=q.device)
     check(library().qs_attention(
         ptr(out), ptr(q), dtype_code(q), out.stride(0), q.stride(0), ptr(k_cache), ptr(v_cache),
         _int32(page_table, "page_table"), page_table.shape[1], page_tokens, _int32(tok_slot, "tok_slot"),
         _int32(tok_pos, "tok_pos"), T, n_heads, n_kv_heads, head_dim, float(scale), int(window),
-        ptr(status), stream()))
+        ptr(status), dv, float(softcap or 0.0), stream()))
+    return out
+
+
+# ------------------------------------------------------------------------------- a 32-bit residual stream, RMS norms
+
+def _code(t) -> int:
+    return dtype_code(t) if t is not None else 0
+
+
+def rmsnorm(x, weight, eps: float, offset: float = 0.0, out_dtype=None, update=None, mult: float = 1.0,
+            want_norm: bool = True):
+    """h = x / sqrt(mean(x^2) + eps) * (offset + weight), statistics in 32-bit; h in `out_dtype` (default: x's).
+    With `update` (a tensor of x's shape): x <- x + mult * update first, in place and in x's type, in the same
+    pass; `want_norm=False` then only updates.  Returns h (None without a norm)."""
+    rows, D, ldx = _rows(x)
+    h = None
+    if want_norm:
+        if weight is None or weight.numel() != D:
+            raise QStreamError(QsError.INVALID_INPUT, f"rmsnorm: width {D} but weight {None if weight is None else tuple(weight.shape)}")
+        h = torch.empty((rows, D), dtype=out_dtype or x.dtype, device=x.device)
+    ldy = 0
+    if update is not None:
+        r2, D2, ldy = _rows(update)
+        if (r2, D2) != (rows, D):
+            raise QStreamError(QsError.INVALID_INPUT, "rmsnorm: the update differs from x in shape")
+    check(library().qs_residual_rmsnorm(ptr(h), _code(h), D, ptr(x) if update is not None else None, ptr(x),
+                                        dtype_code(x), ldx, ptr(update), _code(update), ldy, float(mult),
+                                        ptr(weight) if want_norm else None, _code(weight) if want_norm else 0,
+                                        float(offset), rows, D, float(eps), stream()))
+    return h
+
+
+def gated_group_norm(o, group: int, weight, gate, gate_activation, eps: float, out_dtype) -> torch.Tensor:
+    """out = o / sqrt(mean over each group of `group` consecutive elements of o^2 + eps) * weight * act(gate);
+    group 0: no norm; weight and gate may be None.  Sums in 32-bit."""
+    rows, n, ldi = _rows(o)
+    out = torch.empty((rows, n), dtype=out_dtype, device=o.device)
+    ldg = 0
+    if gate is not None:
+        r2, n2, ldg = _rows(gate)
+        if (r2, n2) != (rows, n):
+            raise QStreamError(QsError.INVALID_INPUT, "gated_group_norm: the gate differs from o in shape")
+    if weight is not None and weight.numel() != n:
+        raise QStreamError(QsError.INVALID_INPUT, f"gated_group_norm: width {n} but weight {tuple(weight.shape)}")
+    check(library().qs_gated_group_norm(ptr(out), dtype_code(out), n, ptr(o), dtype_code(o), ldi, ptr(weight),
+                                        _code(weight), ptr(gate), _code(gate), ldg, ACTIVATIONS[gate_activation],
+                                        rows, n, int(group), float(eps), stream()))
+    return out
+
+
+def gated_act(ab: torch.Tensor, activation) -> torch.Tensor:
+    """out = act(a) * b for ab = [a | b] ([rows, 2 F]), in 32-bit, rounded once."""
+    rows, two_f, ldi = _rows(ab)
+    F = two_f // 2
+    out = torch.empty((rows, F), dtype=ab.dtype, device=ab.device)
+    check(library().qs_gated_act(ptr(out), F, ptr(ab), ldi, dtype_code(ab), rows, F, ACTIVATIONS[activation], stream()))
+    return out
+
+
+def embedding_hashed(table, pair, scale: float, buckets: int, mul_prev: int, mul_cur: int, tokens, tok_slot, tok_pos,
+                     last_token, out_dtype) -> torch.Tensor:
+    """x = table[token] * scale + pair[(previous * mul_prev + token * mul_cur) mod buckets] (row `buckets` for a
+    sequence's first token); `pair` may be None.  `last_token`: int32 [slots, 1], each sequence's last token of
+    earlier steps.  Rows with a negative slot are zero."""
+    V, D = table.shape
+    T = tokens.numel()
+    out = torch.empty((T, D), dtype=out_dtype, device=table.device)
+    if pair is not None and (pair.dtype != table.dtype or pair.shape != (buckets + 1, D)):
+        raise QStreamError(QsError.INVALID_INPUT, "embedding: the pair table does not fit")
+    check(library().qs_embedding_hashed(ptr(out), dtype_code(out), ptr(table), ptr(pair), dtype_code(table), float(scale),
+                                        int(buckets), int(mul_prev), int(mul_cur), _int32(tokens, "tokens"),
+                                        _int32(tok_slot, "tok_slot"), _int32(tok_pos, "tok_pos"),
+                                        ptr(last_token), last_token.stride(0) if last_token is not None else 0,
+                                        T, D, V, stream()))
+    return out
+
+
+def keep_last_rows(dst: torch.Tensor, src: torch.Tensor, seq_start, seq_slot, n_seq: int) -> None:
+    """dst[slot] = the last row of `src` that each sequence of the step brought (rows of whole 4-byte words)."""
+    row_bytes = (src.shape[1] if src.dim() == 2 else 1) * src.element_size()
+    check(library().qs_keep_last_rows(ptr(dst), dst.stride(0) * dst.element_size(), ptr(src),
+                                      src.stride(0) * src.element_size(), row_bytes, _int32(seq_start, "seq_start"),
+                                      _int32(seq_slot, "seq_slot"), int(n_seq), stream()))
+
+
+def state_scan(mode: str, q, k, v, state, seq_start, seq_slot, n_seq, n_heads, key_dim, value_dim, head_decay=None,
+               decay_logits=None, bonus=None, in_activation=None) -> torch.Tensor:
+    """Walk each sequence's tokens of this step through a per-head matrix state (float32 [slots, heads, value_dim,
+    key_dim], updated in place); returns o [T, heads * value_dim] in float32.
+    mode "decay": S <- decay_h S + k v^T, o = S^T q.  mode "wkv": o = (S + diag(bonus) k v^T)^T q, then
+    S <- diag(exp(-exp(decay_logits))) S + k v^T."""
+    T = q.shape[0]
+    o = torch.empty((T, n_heads * value_dim), dtype=torch.float32, device=q.device)
+    if state.dtype != torch.float32 or state.stride(-1) != 1:
+        raise QStreamError(QsError.INVALID_INPUT, "state_scan: the state must be float32")
+    check(library().qs_state_scan(
+        1 if mode == "wkv" else 0, ptr(o), o.stride(0), ptr(q), q.stride(0), ptr(k), k.stride(0), ptr(v), v.stride(0),
+        dtype_code(q), ptr(decay_logits), decay_logits.stride(0) if decay_logits is not None else 0, ptr(head_decay),
+        ptr(bonus), _code(bonus), ptr(state), state.stride(0), _int32(seq_start, "seq_start"),
+        _int32(seq_slot, "seq_slot"), int(n_seq), T, n_heads, key_dim, value_dim, ACTIVATIONS[in_activation], stream()))
+    return o
+
+
+def token_shift(h, mu, last_row, tok_slot, tok_pos) -> torch.Tensor:
+    """out[m] = h + (h shifted down by one token - h) * mu[m]: [n_mix, T, D] in h's type; mu float32 [n_mix, D];
+    `last_row` [slots, D] holds each sequence's last row of earlier steps."""
+    T, D, ldh = _rows(h)
+    n_mix = mu.shape[0]
+    out = torch.empty((n_mix, T, D), dtype=h.dtype, device=h.device)
+    check(library().qs_token_shift(ptr(out), D, T * D, ptr(h), ldh, dtype_code(h), ptr(mu), ptr(last_row),
+                                   last_row.stride(0), _int32(tok_slot, "tok_slot"), _int32(tok_pos, "tok_pos"),
+                                   T, D, n_mix, stream()))
     return out
 
 

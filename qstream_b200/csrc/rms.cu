@@ -1,0 +1,268 @@
+// RMS norms and the small kernels around a residual stream that is kept in 32-bit:
+//
+//   rmsnorm            y = x / sqrt(mean(x^2) + eps) * (offset + w)
+//   residual_rmsnorm   x <- x + mult * y (32-bit, in place), and optionally h = rmsnorm(x) in the same pass
+//   gated_group_norm   out = o / sqrt(mean_group(o^2) + eps) * w * act(gate), groups of consecutive elements
+//                      (one group = the whole row, or one per head; group 0 = no norm, only the gate)
+//   gated_act          out = act(a) * b for the two halves [a | b] of a fused projection (gated feed-forward)
+//   embedding_hashed   x = table[token] * scale + pair_table[hash(previous token, token)]
+//   keep_last_rows     state[slot] = the last row each sequence brought in this step
+//
+// Every sum is taken in 32-bit in a fixed order (block_sum / warp_sum), whatever the storage types.
+#include "common.cuh"
+
+namespace {
+
+// ----------------------------------------------------------------------------- rmsnorm
+
+// One block per row, the row in shared memory as 32-bit floats.  With `y` the row is first updated:
+// x <- x + mult * y, written back to `x_out` (which may be x itself).  `h_out` may be null (update only).
+template <typename TX, typename TY, typename TH>
+__global__ void residual_rmsnorm_kernel(TH* __restrict__ h_out, size_t ldh, TX* x_out, const TX* x, size_t ldx,
+                                        const TY* __restrict__ y, size_t ldy, float mult,
+                                        const void* __restrict__ w, int w_dtype, float offset, int D, float eps) {
+    extern __shared__ float row[];
+    __shared__ float scratch[33];
+    grid_dep_launch();
+    grid_dep_wait();
+    const TX* src = x + (size_t)blockIdx.x * ldx;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        float v = to_f32(src[i]);
+        if (y) {
+            v = fmaf(mult, to_f32(y[(size_t)blockIdx.x * ldy + i]), v);
+            x_out[(size_t)blockIdx.x * ldx + i] = from_f32<TX>(v);
+        }
+        row[i] = v;
+        s = fmaf(v, v, s);
+    }
+    if (!h_out) return;
+    const float rstd = 1.0f / sqrtf(block_sum(s, scratch) / (float)D + eps);
+    TH* dst = h_out + (size_t)blockIdx.x * ldh;
+    for (int i = threadIdx.x; i < D; i += blockDim.x)
+        dst[i] = from_f32<TH>(row[i] * rstd * (offset + load_as_f32(w, w_dtype, i)));
+}
+
+template <typename TX, typename TY, typename TH>
+int launch_norm(void* h_out, long long ldh, void* x_out, const void* x, long long ldx, const void* y, long long ldy,
+                float mult, const void* w, int w_dtype, float offset, int rows, int D, float eps, cudaStream_t stream) {
+    const size_t smem = (size_t)D * sizeof(float);
+    const int threads = D >= 4096 ? 512 : (D >= 1024 ? 256 : 128);
+    auto kernel = residual_rmsnorm_kernel<TX, TY, TH>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "rmsnorm: %s", cudaGetErrorString(e));
+    }
+    cudaError_t e = qs_launch_dependent(kernel, dim3(rows), dim3(threads), smem, stream, (TH*)h_out, (size_t)ldh,
+                                        (TX*)x_out, (const TX*)x, (size_t)ldx, (const TY*)y, (size_t)ldy, mult, w, w_dtype,
+                                        offset, D, eps);
+    if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "rmsnorm: %s", cudaGetErrorString(e));
+    return qs_check_launch("rmsnorm");
+}
+
+// ----------------------------------------------------------------------------- gated group norm
+
+// One block per row.  group == n: one norm over the row (block sum).  0 < group < n: a warp per group, groups dealt
+// to the warps in turn.  group == 0: no norm.  Then * w[c] (if given) * act(gate[c]) (if given).
+template <typename TI, typename TG, typename TO>
+__global__ void gated_group_norm_kernel(TO* __restrict__ out, size_t ldo, const TI* __restrict__ o, size_t ldi,
+                                        const void* __restrict__ w, int w_dtype, const TG* __restrict__ gate, size_t ldg,
+                                        int gate_act, int n, int group, float eps) {
+    extern __shared__ float rstd_of[];               // one per group (at least one)
+    __shared__ float scratch[33];
+    grid_dep_launch();
+    grid_dep_wait();
+    const TI* src = o + (size_t)blockIdx.x * ldi;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    if (group == n) {
+        float s = 0.f;
+        for (int i = threadIdx.x; i < n; i += blockDim.x) { const float v = to_f32(src[i]); s = fmaf(v, v, s); }
+        const float total = block_sum(s, scratch);
+        if (threadIdx.x == 0) rstd_of[0] = 1.0f / sqrtf(total / (float)n + eps);
+    } else if (group > 0) {
+        for (int g = warp; g * group < n; g += warps) {
+            float s = 0.f;
+            for (int i = lane; i < group; i += 32) { const float v = to_f32(src[g * group + i]); s = fmaf(v, v, s); }
+            s = warp_sum(s);
+            if (lane == 0) rstd_of[g] = 1.0f / sqrtf(s / (float)group + eps);
+        }
+    }
+    __syncthreads();
+    TO* dst = out + (size_t)blockIdx.x * ldo;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        float v = to_f32(src[i]);
+        if (group > 0) v *= rstd_of[i / group];
+        if (w) v *= load_as_f32(w, w_dtype, i);
+        if (gate) v *= apply_activation(to_f32(gate[(size_t)blockIdx.x * ldg + i]), gate_act);
+        dst[i] = from_f32<TO>(v);
+    }
+}
+
+template <typename TI, typename TG, typename TO>
+int launch_gated(void* out, long long ldo, const void* o, long long ldi, const void* w, int w_dtype, const void* gate,
+                 long long ldg, int gate_act, int rows, int n, int group, float eps, cudaStream_t stream) {
+    const int n_groups = group > 0 ? n / group : 1;
+    const int threads = n >= 2048 ? 256 : 128;
+    cudaError_t e = qs_launch_dependent(gated_group_norm_kernel<TI, TG, TO>, dim3(rows), dim3(threads),
+                                        (size_t)n_groups * sizeof(float), stream, (TO*)out, (size_t)ldo, (const TI*)o,
+                                        (size_t)ldi, w, w_dtype, (const TG*)gate, (size_t)ldg, gate_act, n, group, eps);
+    if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "gated_group_norm: %s", cudaGetErrorString(e));
+    return qs_check_launch("gated_group_norm");
+}
+
+// ----------------------------------------------------------------------------- gated activation
+
+template <typename T>
+__global__ void gated_act_kernel(T* __restrict__ out, size_t ldo, const T* __restrict__ ab, size_t ldi, int F, int act,
+                                 size_t total) {
+    grid_dep_launch();
+    grid_dep_wait();
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = e / F;
+        const int c = (int)(e - r * F);
+        const float a = to_f32(ab[r * ldi + c]), b = to_f32(ab[r * ldi + F + c]);
+        out[r * ldo + c] = from_f32<T>(apply_activation(a, act) * b);
+    }
+}
+
+// ----------------------------------------------------------------------------- hashed-pair embedding
+
+// x[t] = table[token] * scale + pair[row], row = (previous * mul_prev + token * mul_cur) mod buckets, and row
+// `buckets` for a sequence's first token.  The previous token is the row above if it belongs to the same
+// sequence, else what the sequence's earlier steps left in `last_token[slot]`.
+template <typename TO, typename TT>
+__global__ void embedding_hashed_kernel(TO* __restrict__ out, const TT* __restrict__ table, float scale,
+                                        const TT* __restrict__ pair, long long buckets, long long mul_prev,
+                                        long long mul_cur, const int32_t* __restrict__ tokens,
+                                        const int32_t* __restrict__ tok_slot, const int32_t* __restrict__ tok_pos,
+                                        const int32_t* __restrict__ last_token, size_t ld_last, int D, int V) {
+    const int t = blockIdx.x;
+    TO* dst = out + (size_t)t * D;
+    const int slot = tok_slot[t];
+    if (slot < 0) {
+        for (int i = threadIdx.x; i < D; i += blockDim.x) dst[i] = from_f32<TO>(0.f);
+        return;
+    }
+    int id = tokens[t];
+    id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+    const TT* row = table + (size_t)id * D;
+    const TT* prow = nullptr;
+    if (pair) {
+        long long r = buckets;
+        if (tok_pos[t] > 0) {
+            int prev = (t > 0 && tok_slot[t - 1] == slot) ? tokens[t - 1] : last_token[(size_t)slot * ld_last];
+            prev = prev < 0 ? 0 : (prev >= V ? V - 1 : prev);
+            r = ((long long)prev * mul_prev + (long long)id * mul_cur) % buckets;
+            if (r < 0) r += buckets;
+        }
+        prow = pair + (size_t)r * D;
+    }
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        float v = to_f32(row[i]) * scale;
+        if (prow) v += to_f32(prow[i]);
+        dst[i] = from_f32<TO>(v);
+    }
+}
+
+// ----------------------------------------------------------------------------- keep last rows
+
+// dst[slot] = the last row that each sequence of the step brought (rows of `row_bytes` bytes, 4-byte words).
+__global__ void keep_last_rows_kernel(uint32_t* __restrict__ dst, size_t dst_words, const uint32_t* __restrict__ src,
+                                      size_t src_words, int row_words, const int32_t* __restrict__ seq_start,
+                                      const int32_t* __restrict__ seq_slot) {
+    const int s = blockIdx.x;
+    const int slot = seq_slot[s];
+    const int a = seq_start[s], b = seq_start[s + 1];
+    if (slot < 0 || b <= a) return;
+    const uint32_t* from = src + (size_t)(b - 1) * src_words;
+    uint32_t* to = dst + (size_t)slot * dst_words;
+    for (int i = threadIdx.x; i < row_words; i += blockDim.x) to[i] = from[i];
+}
+
+}  // namespace
+
+// h = rmsnorm(x) (y == null), or x_out = x + mult * y and h = rmsnorm(x_out) (h_out may then be null).
+QS_API int qs_residual_rmsnorm(void* h_out, int h_dtype, long long ldh, void* x_out, const void* x, int x_dtype,
+                               long long ldx, const void* y, int y_dtype, long long ldy, float mult, const void* w,
+                               int w_dtype, float offset, int rows, int D, float eps, cudaStream_t stream) {
+    if (rows == 0) return QS_OK;
+    QS_REQUIRE(rows > 0 && D > 0, "rmsnorm: bad sizes rows=%d D=%d", rows, D);
+    QS_REQUIRE(h_out || y, "rmsnorm: nothing to do");
+    QS_REQUIRE(!h_out || w, "rmsnorm: a norm without a weight");
+    QS_REQUIRE(!y || x_out, "rmsnorm: an update with nowhere to go");
+    QS_REQUIRE((size_t)D * sizeof(float) <= 200 * 1024, "rmsnorm: width %d does not fit one block's shared memory", D);
+    typedef __nv_bfloat16 bf16;
+#define GO(TX, TY, TH) return launch_norm<TX, TY, TH>(h_out, ldh, x_out, x, ldx, y, ldy, mult, w, w_dtype, offset, rows, D, eps, stream)
+    if (!y) y_dtype = x_dtype;
+    if (!h_out) h_dtype = x_dtype;
+    if (x_dtype == QS_F32 && y_dtype == QS_F32 && h_dtype == QS_F32) GO(float, float, float);
+    if (x_dtype == QS_F32 && y_dtype == QS_F32 && h_dtype == QS_BF16) GO(float, float, bf16);
+    if (x_dtype == QS_F32 && y_dtype == QS_BF16 && h_dtype == QS_BF16) GO(float, bf16, bf16);
+    if (x_dtype == QS_F32 && y_dtype == QS_BF16 && h_dtype == QS_F32) GO(float, bf16, float);
+    if (x_dtype == QS_BF16 && y_dtype == QS_BF16 && h_dtype == QS_BF16) GO(bf16, bf16, bf16);
+#undef GO
+    return qs_fail(QS_ERR_INVALID_INPUT, "rmsnorm: unsupported types x=%d y=%d h=%d", x_dtype, y_dtype, h_dtype);
+}
+
+QS_API int qs_gated_group_norm(void* out, int out_dtype, long long ldo, const void* o, int o_dtype, long long ldi,
+                               const void* w, int w_dtype, const void* gate, int gate_dtype, long long ldg,
+                               int gate_act, int rows, int n, int group, float eps, cudaStream_t stream) {
+    if (rows == 0) return QS_OK;
+    QS_REQUIRE(rows > 0 && n > 0 && group >= 0 && (group == 0 || n % group == 0),
+               "gated_group_norm: bad sizes rows=%d n=%d group=%d", rows, n, group);
+    typedef __nv_bfloat16 bf16;
+    if (!gate) gate_dtype = out_dtype;
+#define GO(TI, TG, TO) return launch_gated<TI, TG, TO>(out, ldo, o, ldi, w, w_dtype, gate, ldg, gate_act, rows, n, group, eps, stream)
+    if (o_dtype == QS_F32 && gate_dtype == QS_F32 && out_dtype == QS_F32) GO(float, float, float);
+    if (o_dtype == QS_F32 && gate_dtype == QS_BF16 && out_dtype == QS_BF16) GO(float, bf16, bf16);
+    if (o_dtype == QS_BF16 && gate_dtype == QS_BF16 && out_dtype == QS_BF16) GO(bf16, bf16, bf16);
+#undef GO
+    return qs_fail(QS_ERR_INVALID_INPUT, "gated_group_norm: unsupported types o=%d gate=%d out=%d", o_dtype, gate_dtype, out_dtype);
+}
+
+QS_API int qs_gated_act(void* out, long long ldo, const void* ab, long long ldi, int dtype, int rows, int F, int act,
+                        cudaStream_t stream) {
+    if (rows == 0) return QS_OK;
+    QS_REQUIRE(rows > 0 && F > 0 && ldi >= 2 * (long long)F && ldo >= F, "gated_act: bad sizes rows=%d F=%d", rows, F);
+    const size_t total = (size_t)rows * F;
+    const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+    cudaError_t e;
+    if (dtype == QS_F32)
+        e = qs_launch_dependent(gated_act_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)out, (size_t)ldo,
+                                (const float*)ab, (size_t)ldi, F, act, total);
+    else if (dtype == QS_BF16)
+        e = qs_launch_dependent(gated_act_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)out,
+                                (size_t)ldo, (const __nv_bfloat16*)ab, (size_t)ldi, F, act, total);
+    else return qs_fail(QS_ERR_INVALID_INPUT, "gated_act: unknown dtype %d", dtype);
+    if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "gated_act: %s", cudaGetErrorString(e));
+    return qs_check_launch("gated_act");
+}
+
+QS_API int qs_embedding_hashed(void* out, int out_dtype, const void* table, const void* pair, int table_dtype, float scale,
+                               long long buckets, long long mul_prev, long long mul_cur, const int32_t* tokens,
+                               const int32_t* tok_slot, const int32_t* tok_pos, const int32_t* last_token, long long ld_last,
+                               int T, int D, int V, cudaStream_t stream) {
+    if (T == 0) return QS_OK;
+    QS_REQUIRE(T > 0 && D > 0 && V > 0, "embedding: bad sizes T=%d D=%d V=%d", T, D, V);
+    QS_REQUIRE(!pair || (buckets > 0 && last_token), "embedding: a pair table needs buckets and the sequences' last tokens");
+    const int threads = D >= 1024 ? 256 : 128;
+#define LAUNCH(TO, TT) embedding_hashed_kernel<TO, TT><<<T, threads, 0, stream>>>((TO*)out, (const TT*)table, scale, \
+        (const TT*)pair, buckets, mul_prev, mul_cur, tokens, tok_slot, tok_pos, last_token, (size_t)ld_last, D, V)
+    if (out_dtype == QS_F32 && table_dtype == QS_F32) LAUNCH(float, float);
+    else if (out_dtype == QS_F32 && table_dtype == QS_BF16) LAUNCH(float, __nv_bfloat16);
+    else if (out_dtype == QS_BF16 && table_dtype == QS_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else return qs_fail(QS_ERR_INVALID_INPUT, "embedding: unsupported types out=%d table=%d", out_dtype, table_dtype);
+#undef LAUNCH
+    return qs_check_launch("embedding_hashed");
+}
+
+QS_API int qs_keep_last_rows(void* dst, long long dst_bytes, const void* src, long long src_bytes, int row_bytes,
+                             const int32_t* seq_start, const int32_t* seq_slot, int n_seq, cudaStream_t stream) {
+    if (n_seq == 0) return QS_OK;
+    QS_REQUIRE(n_seq > 0 && row_bytes > 0 && row_bytes % 4 == 0 && dst_bytes % 4 == 0 && src_bytes % 4 == 0 &&
+               ((uintptr_t)dst % 4) == 0 && ((uintptr_t)src % 4) == 0, "keep_last_rows: rows must be whole 4-byte words");
+    const int words = row_bytes / 4;
+    keep_last_rows_kernel<<<n_seq, words >= 256 ? 256 : (words >= 64 ? 64 : 32), 0, stream>>>(
+        (uint32_t*)dst, (size_t)dst_bytes / 4, (const uint32_t*)src, (size_t)src_bytes / 4, words, seq_start, seq_slot);
+    return qs_check_launch("keep_last_rows");
+}

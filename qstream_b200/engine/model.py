@@ -151,8 +151,14 @@ class CausalLM:
     def kv_needs(self) -> dict[int, KvNeed]:
         return {cid: part.kv_need() for _, cid, part in self._cache_users() if part.kv_need() is not None}
 
-    def state_needs(self) -> dict[int, StateNeed]:
-        return {cid: part.state_need() for _, cid, part in self._cache_users() if part.state_need() is not None}
+    def state_needs(self) -> dict:
+        """Cache entry id -> what its part keeps per sequence (a StateNeed or a mapping name -> StateNeed); the
+        embedding's state, if it keeps any, lies under the key "embedding"."""
+        needs = {cid: part.state_need() for _, cid, part in self._cache_users() if part.state_need() is not None}
+        own = getattr(self.embedding, "state_need", lambda: None)()
+        if own is not None:
+            needs["embedding"] = own
+        return needs
 
     # ------------------------------------------------------------------ forward
     def forward(self, step) -> torch.Tensor | None:

@@ -91,13 +91,16 @@ class StepContext:
         self.side_stream = side_stream
         # int32 [4] on the device when every layer's output is to be scanned for values that are not finite
         self.nan_record = nan_record
+        # what one layer leaves for later layers of the same step (tensors of the step's tokens)
+        self.scratch = {}
 
     def kv(self, cache_id: int):
         return self.cache.view(cache_id)
 
-    def state(self, cache_id: int) -> Optional[torch.Tensor]:
-        """The state tensor [slots, *shape] of a cache entry (None if it has none)."""
-        return self.cache.state.get(cache_id)
+    def state(self, cache_id, name=None) -> Optional[torch.Tensor]:
+        """The state tensor [slots, *shape] of a cache entry (None if it has none); `name` picks one where the
+        entry's part asked for several."""
+        return self.cache.state.get(cache_id, name)
 
 
 STATUS_MESSAGES = {
@@ -157,7 +160,7 @@ class Engine:
 
     def _check_budget(self, kv_needs, max_tokens, mem_budget=0):
         elem = torch.empty((), dtype=self.dtype).element_size()
-        want = sum(2 * max_tokens * n.n_kv_heads * n.head_dim * elem for n in kv_needs.values())
+        want = sum(max_tokens * n.n_kv_heads * (n.head_dim + n.value_dim) * elem for n in kv_needs.values())
         if mem_budget and want > mem_budget:
             raise QStreamError(QsError.BUDGET_EXCEEDED,
                                f"a cache of {max_tokens} tokens needs {want / 2**20:.1f} MiB, "

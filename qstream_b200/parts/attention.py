@@ -5,6 +5,11 @@ the keys are kept (:871-880), scores q.k / sqrt(dh) over the keys up to the toke
 position, softmax, weighted sum of values (:888-922), heads concatenated, output
 projection (:926-934).  Query head j reads key head j // (H / Hkv) (:884,889).  The
 three projections are one matrix product over the concatenated weights.
+
+Options a spec may switch on, each with its constants as the spec's fields: values with a head size of
+their own; a factor on the scores other than head_dim^-1/2; a tanh cap on the scores; values blended
+with those that an earlier layer computed for the same token (what is cached is the blend); a sigmoid gate
+from the mixer's input on the concatenated heads (its projection rides in the same product as q, k, v).
 """
 from __future__ import annotations
 
@@ -24,15 +29,20 @@ class Attention(Mixer):
     @classmethod
     def declare(cls, spec):
         hq, hkv = spec.n_heads * spec.head_dim, spec.n_kv_heads * spec.head_dim
-        d = {"q": TensorDecl((hq, spec.width)), "out": TensorDecl((spec.width, hq))}
+        ho, hv = spec.n_heads * spec.value_dim, spec.n_kv_heads * spec.value_dim
+        d = {"q": TensorDecl((hq, spec.width)), "out": TensorDecl((spec.width, ho))}
         if not spec.shares_cache:
             d["k"] = TensorDecl((hkv, spec.width))
-            d["v"] = TensorDecl((hkv, spec.width))
+            d["v"] = TensorDecl((hv, spec.width))
         if spec.qkv_bias:
             d["q_bias"] = TensorDecl((hq,), "bias")
             if not spec.shares_cache:
                 d["k_bias"] = TensorDecl((hkv,), "bias")
-                d["v_bias"] = TensorDecl((hkv,), "bias")
+                d["v_bias"] = TensorDecl((hv,), "bias")
+        if spec.gate:
+            d["gate"] = TensorDecl((ho, spec.width))
+        if spec.value_mix is not None:
+            d["value_mix"] = TensorDecl((), "fraction")
         if spec.out_bias:
             d["out_bias"] = TensorDecl((spec.width,), "bias")
         return d
@@ -42,17 +52,24 @@ class Attention(Mixer):
         if spec.n_heads % spec.n_kv_heads:
             raise QStreamError(QsError.INVALID_MODEL,
                                f"{spec.n_heads} query heads are no multiple of {spec.n_kv_heads} key heads")
-        if spec.head_dim % 16:
+        if spec.head_dim % 2 or spec.head_dim > 512 or spec.value_dim > 512:
             raise QStreamError(QsError.UNSUPPORTED_ARCH,
-                               f"attention kernels take head sizes in steps of 16, not {spec.head_dim}")
+                               f"attention kernels take even head sizes up to 512, not {spec.head_dim} / {spec.value_dim}")
+        if spec.value_mix not in (None, "first", "blend") or (spec.value_mix and spec.shares_cache):
+            raise QStreamError(QsError.INVALID_MODEL, f"attention: value_mix '{spec.value_mix}' does not fit")
         names = ["q"] if spec.shares_cache else ["q", "k", "v"]
-        mats = [tensors[n] for n in names]
+        mats = [tensors[n] for n in names] + ([tensors["gate"]] if spec.gate else [])
         if len({m.dtype for m in mats}) != 1:
             raise QStreamError(QsError.INVALID_MODEL, "q/k/v projections are stored in different types")
         self.w_qkv = torch.cat(mats, dim=0).contiguous() if len(mats) > 1 else mats[0]
         self.b_qkv = None
         if spec.qkv_bias:
-            self.b_qkv = torch.cat([tensors[n + "_bias"].float() for n in names]).contiguous()
+            biases = [tensors[n + "_bias"].float() for n in names]
+            if spec.gate:                               # the gate's rows of the product have no bias
+                biases.append(torch.zeros(tensors["gate"].shape[0], dtype=torch.float32, device=biases[0].device))
+            self.b_qkv = torch.cat(biases).contiguous()
+        # the blend's weight is a constant of the model: read once, passed to the kernel by value
+        self.value_mix = float(tensors["value_mix"].float().item()) if spec.value_mix == "blend" else 0.0
         self.w_out = tensors["out"]
         self.b_out = tensors.get("out_bias") if spec.out_bias else None
         self.position = None
@@ -62,17 +79,18 @@ class Attention(Mixer):
     @property
     def cache_bytes_per_key(self) -> int:
         """What one key of a sequence costs a decode step to read: its key and its value, all heads."""
-        return 2 * self.spec.n_kv_heads * self.spec.head_dim * self.w_qkv.element_size()
+        return self.spec.n_kv_heads * (self.spec.head_dim + self.spec.value_dim) * self.w_qkv.element_size()
 
     def kv_need(self):
         if self.spec.shares_cache:
             return None
         s = self.spec
-        return KvNeed(n_kv_heads=s.n_kv_heads, head_dim=s.head_dim, window=s.window)
+        return KvNeed(n_kv_heads=s.n_kv_heads, head_dim=s.head_dim, window=s.window,
+                      v_head_dim=0 if s.value_dim == s.head_dim else s.value_dim)
 
-    def forward(self, h, step, cache_id, residuals=()):
+    def forward(self, h, step, cache_id, residuals=(), out_dtype=None):
         o = self.forward_hidden(h, step, cache_id)
-        return linear(o, self.w_out, self.b_out, residuals=residuals)
+        return linear(o, self.w_out, self.b_out, residuals=residuals, out_dtype=out_dtype)
 
     # A parallel block may fuse this part's output projection with the feed-forward's down projection:
     # it takes the projection from `output_projection()` and calls `forward_hidden` with a view to fill.
@@ -80,13 +98,15 @@ class Attention(Mixer):
         return self.w_out, self.b_out
 
     def forward_hidden(self, h, step, cache_id, out=None):
-        """Everything before the output projection: [T, n_heads * head_dim], written to `out` if given."""
+        """Everything before the output projection: [T, n_heads * value_dim], written to `out` if given."""
         s = self.spec
         b = step.batch
         view = step.kv(cache_id)
-        hq, hkv = s.n_heads * s.head_dim, s.n_kv_heads * s.head_dim
+        hq, hkv, hv = s.n_heads * s.head_dim, s.n_kv_heads * s.head_dim, s.n_kv_heads * s.value_dim
         qkv = linear(h, self.w_qkv, self.b_qkv)
         q = qkv[:, :hq]
+        if s.gate and out is not None:
+            raise QStreamError(QsError.INVALID_INPUT, "attention: a gated mixer writes its own output")
         table = getattr(self.position, "fused_table", None) if self.position is not None else None
         if s.shares_cache:
             if self.position is not None:
@@ -98,14 +118,25 @@ class Attention(Mixer):
                                    step.status, settled=True)
         else:
             k = qkv[:, hq:hq + hkv]
-            v = qkv[:, hq + hkv:]
+            v = qkv[:, hq + hkv:hq + hkv + hv]
+            v_first = None
+            if s.value_mix == "first":
+                step.scratch["value_mix"] = v               # later layers of this step blend their values with these
+            elif s.value_mix == "blend":
+                v_first = step.scratch.get("value_mix")
+                if v_first is None or v_first.shape != v.shape:
+                    raise QStreamError(QsError.INVALID_MODEL, "attention: values to blend with, but no earlier layer kept any of this shape")
             if self.position is not None and table is None:
                 self.position.apply(q, k, step, s.n_heads, s.n_kv_heads, s.head_dim)
             ops.rope_store(q, k, v, s.n_heads, s.n_kv_heads, s.head_dim,
                            getattr(self.position, "rotary_dim", 0) if table is not None else 0, table,
                            b.tok_slot, b.tok_pos, view.page_table, view.page_tokens, view.k, view.v,
-                           step.status, settled=True)     # a step's slots, positions and pages arrive before its first kernel
-        return attend(q, s, step, view, out)
+                           step.status, settled=True,     # a step's slots, positions and pages arrive before its first kernel
+                           v_head_dim=s.value_dim, v_first=v_first, v_mix=self.value_mix)
+        o = attend(q, s, step, view, out)
+        if s.gate:
+            o = ops.gated_group_norm(o, 0, None, qkv[:, qkv.shape[1] - s.n_heads * s.value_dim:], "sigmoid", 0.0, o.dtype)
+        return o
 
 
 def attend(q, spec, step, view, out=None):
@@ -119,7 +150,7 @@ def attend(q, spec, step, view, out=None):
             return done
     return ops.attention(q, spec.n_heads, spec.n_kv_heads, spec.head_dim, spec.scale, spec.window,
                          b.tok_slot, b.tok_pos, view.page_table, view.page_tokens, view.k, view.v,
-                         step.status, out=out)
+                         step.status, out=out, v_head_dim=spec.value_dim, softcap=spec.softcap)
 
 
 register("mixer", "attention", Attention)

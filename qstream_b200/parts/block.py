@@ -29,7 +29,8 @@ class Arrangement(Part):
         position = getattr(self.mixer, "position", None)
         self.captures_any_step = self.captures_own_step and all(
             getattr(p, "captures_any_step", False)
-            for p in (self.mixer, self.ffn, *self.norms.values(), *([position] if position else [])))
+            for p in (self.mixer, *([self.ffn] if self.ffn is not None else []), *self.norms.values(),
+                      *([position] if position else [])))
         missing = [n for n in self.norm_names if n not in self.norms]
         if missing:
             raise QStreamError(QsError.INVALID_MODEL,
@@ -147,8 +148,56 @@ class SequentialBlock(Arrangement):
         return self.ffn.forward(self.norms["post_mixer"].forward(x), step, residuals=(x,))
 
 
+class ScaledResidualBlock(Arrangement):
+    """x += m mixer(norm_1(x)); x += m ffn(norm_2(x)), with the residual stream x in 32-bit whatever the engine's
+    type (the embedding delivers it so) and updated in place; a layer may have no feed-forward.  The branches'
+    results arrive in 32-bit from their last product; the update x + m y and the norm that follows it are one
+    kernel.  Norms must offer `forward_update` (the RMS norm does)."""
+    norm_names = ("input",)
+
+    def __init__(self, spec, parts, runtime):
+        super().__init__(spec, parts, runtime)
+        import inspect
+        import torch
+        if self.ffn is not None and "post_mixer" not in self.norms:
+            raise QStreamError(QsError.INVALID_MODEL, "a scaled-residual layer with a feed-forward needs the norm 'post_mixer'")
+        self.mult = float(spec.residual_scale)
+        self.wide = torch.float32
+        # parts of another make (a test's toy mixer) may not take `out_dtype`; their result is used as it comes
+        self._typed = {id(p): "out_dtype" in inspect.signature(p.forward).parameters for p in (self.mixer, self.ffn) if p}
+
+    @classmethod
+    def part_specs(cls, spec):
+        yield "mixer", spec.mixer
+        if spec.ffn is not None:
+            yield "feed_forward", spec.ffn
+        for norm_spec in spec.norms.values():
+            yield "norm", norm_spec
+
+    @classmethod
+    def build(cls, spec, make, runtime):
+        parts = {"mixer": make("mixer", spec.mixer), "ffn": make("feed_forward", spec.ffn) if spec.ffn is not None else None,
+                 "norms": {name: make("norm", ns) for name, ns in spec.norms.items()}}
+        return cls(spec, parts, runtime)
+
+    def _wide(self, part):
+        return {"out_dtype": self.wide} if self._typed[id(part)] else {}
+
+    def forward(self, x, step, cache_id):
+        from ..csrc import ops
+        y = self.mixer.forward(self.norms["input"].forward(x), step, cache_id, **self._wide(self.mixer))
+        if self.ffn is None:
+            ops.rmsnorm(x, None, 0.0, update=y, mult=self.mult, want_norm=False)
+            return x
+        h = self.norms["post_mixer"].forward_update(x, y, self.mult)
+        z = self.ffn.forward(h, step, **self._wide(self.ffn))
+        ops.rmsnorm(x, None, 0.0, update=z, mult=self.mult, want_norm=False)
+        return x
+
+
 register("arrangement", "parallel", ParallelBlock)
 register("arrangement", "sequential", SequentialBlock)
+register("arrangement", "scaled_residual", ScaledResidualBlock)
 
 
 def build_block(spec, tensors_of, runtime):

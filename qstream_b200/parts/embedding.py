@@ -1,4 +1,5 @@
-"""Token embedding: x[t] = table[token[t]], no position term, no scale (QStream src/engine.c:710-765)."""
+"""Token embeddings: the plain table x[t] = table[token[t]], no position term, no scale (QStream
+src/engine.c:710-765), and a scaled table with a second, hashed table of token pairs."""
 from __future__ import annotations
 
 from ..csrc import ops
@@ -21,4 +22,41 @@ class TokenEmbedding(Embedding):
         return ops.embedding(self.weight, step.batch.tokens, self.runtime.dtype)
 
 
+class PairEmbedding(Embedding):
+    """x = table[token] * scale + pair[hash(previous token, token)]: a second table indexed by a hash of the
+    token and the one before it (its last row for a sequence's first token).  The previous token of a sequence
+    whose earlier tokens came in earlier steps is state: one int32 per slot, kept after every step.  The
+    result may be wider than the engine's type (a 32-bit residual stream)."""
+    captures_any_step = True
+
+    @classmethod
+    def declare(cls, spec):
+        d = {"weight": TensorDecl((spec.vocab_size, spec.width))}
+        if spec.buckets:
+            d["pair"] = TensorDecl((spec.buckets + 1, spec.width))
+        return d
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        import torch
+        self.weight = tensors["weight"]
+        self.pair = tensors["pair"] if spec.buckets else None
+        self.out_dtype = {"float32": torch.float32, "bfloat16": torch.bfloat16, None: runtime.dtype}[spec.stream_dtype]
+
+    def state_need(self):
+        import torch
+        from ..cache import StateNeed
+        return StateNeed((1,), torch.int32) if self.pair is not None else None
+
+    def forward(self, step):
+        b, s = step.batch, self.spec
+        last = step.state("embedding") if self.pair is not None else None
+        x = ops.embedding_hashed(self.weight, self.pair, s.scale, s.buckets, s.mul_prev, s.mul_cur, b.tokens,
+                                 b.tok_slot, b.tok_pos, last, self.out_dtype)
+        if last is not None:        # after the lookup has read it: the token each sequence ends this step with
+            ops.keep_last_rows(last, b.tokens.view(-1, 1), b.seq_start, b.seq_slot, b.n_seq)
+        return x
+
+
 register("embedding", "embedding", TokenEmbedding)
+register("embedding", "pair_embedding", PairEmbedding)

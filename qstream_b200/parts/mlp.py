@@ -43,4 +43,29 @@ class Mlp(FeedForward):
         return linear(h, self.up, self.up_bias, activation=self.spec.activation, out=out)
 
 
+class GatedMlp(FeedForward):
+    """down(act(gate h) * (up h)), no biases: gate and up are one product over the stacked weights, the
+    activation and the product of the halves one kernel in 32-bit (the reference's llama feed-forward,
+    QStream src/engine.c:1115-1148)."""
+    captures_any_step = True
+
+    @classmethod
+    def declare(cls, spec):
+        return {"gate": TensorDecl((spec.inner, spec.width)), "up": TensorDecl((spec.inner, spec.width)),
+                "down": TensorDecl((spec.width, spec.inner))}
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        import torch
+        if spec.activation not in ops.ACTIVATIONS:
+            raise QStreamError(QsError.UNSUPPORTED_ARCH, f"activation '{spec.activation}' has no kernel")
+        self.gate_up = torch.cat([tensors["gate"], tensors["up"]], dim=0).contiguous()
+        self.down = tensors["down"]
+
+    def forward(self, h, step, residuals=(), out_dtype=None):
+        g = ops.gated_act(linear(h, self.gate_up), self.spec.activation)
+        return linear(g, self.down, None, residuals=residuals, out_dtype=out_dtype)
+
+
 register("feed_forward", "mlp", Mlp)
+register("feed_forward", "gated_mlp", GatedMlp)

@@ -1,4 +1,6 @@
-"""LayerNorm with weight and optional bias (QStream src/kernels_scalar.c:151-171)."""
+"""LayerNorm with weight and optional bias (QStream src/kernels_scalar.c:151-171), and the RMS norm
+x / sqrt(mean(x^2) + eps) * (offset + weight) (the reference's `rmsnorm`, src/kernels_scalar.c:173-186, has
+offset 0; weights stored around zero take offset 1)."""
 from __future__ import annotations
 
 from ..csrc import ops
@@ -26,4 +28,27 @@ class LayerNorm(Norm):
         return ops.layernorm(x, self.weight, self.bias, self.eps, settled=True)     # a model's weights are old
 
 
+class RmsNorm(Norm):
+    """Reads x in its own type (a 32-bit residual stream in a bfloat16 engine, for instance) and writes the
+    engine's type.  `forward_update` first adds a scaled branch to x, in place, in the same kernel."""
+    captures_any_step = True
+
+    @classmethod
+    def declare(cls, spec):
+        return {"weight": TensorDecl((spec.size,), "norm_delta" if spec.offset else "norm_weight")}
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.weight = tensors["weight"]
+        self.eps, self.offset = float(spec.eps), float(spec.offset)
+
+    def forward(self, x):
+        return ops.rmsnorm(x, self.weight, self.eps, self.offset, out_dtype=self.runtime.dtype)
+
+    def forward_update(self, x, branch, mult):
+        """x <- x + mult * branch (in place), then the norm of the new x."""
+        return ops.rmsnorm(x, self.weight, self.eps, self.offset, out_dtype=self.runtime.dtype, update=branch, mult=mult)
+
+
 register("norm", "layernorm", LayerNorm)
+register("norm", "rmsnorm", RmsNorm)

@@ -13,18 +13,27 @@ from ..csrc import ops
 from .base import PositionEncoding, register
 
 
+_TABLES: dict = {}      # layers with the same rotation share one table
+
+
+def _table(rotary_dim: int, base: float, max_positions: int, device):
+    key = (rotary_dim, float(base), int(max_positions), str(device))
+    if key not in _TABLES:
+        i = torch.arange(0, rotary_dim, 2, dtype=torch.float64)
+        freq = torch.pow(torch.tensor(float(base), dtype=torch.float64), -i / max(rotary_dim, 1))
+        ang = torch.arange(max_positions, dtype=torch.float64)[:, None] * freq[None, :]
+        _TABLES[key] = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).to(torch.float32).contiguous().to(device)
+    return _TABLES[key]
+
+
 class RotaryInterleaved(PositionEncoding):
     captures_any_step = True
 
     def __init__(self, spec, tensors, runtime):
         super().__init__(spec, tensors, runtime)
         self.rotary_dim = int(spec.rotary_dim)
-        i = torch.arange(0, self.rotary_dim, 2, dtype=torch.float64)
-        freq = torch.pow(torch.tensor(float(spec.base), dtype=torch.float64), -i / max(self.rotary_dim, 1))
-        ang = torch.arange(spec.max_positions, dtype=torch.float64)[:, None] * freq[None, :]
-        table = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).to(torch.float32)
         # Attention fuses the rotation with its cache write when a position part offers this.
-        self.fused_table = table.contiguous().to(runtime.device) if self.rotary_dim > 0 else None
+        self.fused_table = _table(self.rotary_dim, spec.base, spec.max_positions, runtime.device) if self.rotary_dim > 0 else None
 
     def apply(self, q, k, step, n_heads, n_kv_heads, head_dim):
         """Rotate q and k in place (no cache write); for mixers that do not fuse the rotation with

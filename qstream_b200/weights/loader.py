@@ -36,7 +36,9 @@ from .safetensors_io import SafetensorsFile
 @dataclass(frozen=True)
 class TensorDecl:
     """A tensor a part wants.  `role` tells the random initialiser what it is:
-    "matrix" (projection or table), "norm_weight", "bias" or "int_table"."""
+    "matrix" (projection or table), "norm_weight" (around one), "norm_delta" (a norm weight stored around zero),
+    "bias", "fraction" (a blend weight between 0 and 1) or "int_table".  A size of -1 in `shape` stands for
+    whatever the checkpoint holds there."""
     shape: tuple
     role: str = "matrix"
 
@@ -118,7 +120,7 @@ def bind_tensors(files: list[SafetensorsFile], wanted: Mapping[str, TensorDecl],
         if name not in where:
             continue
         e = where[name].entries[name]
-        if tuple(e.shape) != tuple(decl.shape):
+        if len(e.shape) != len(decl.shape) or any(w >= 0 and w != f for f, w in zip(e.shape, decl.shape)):
             wrong.append(f"{name}: file has {list(e.shape)}, model wants {list(decl.shape)}")
         elif decl.is_int == e.dtype.is_floating_point:
             wrong.append(f"{name}: file stores {e.dtype}, model wants "

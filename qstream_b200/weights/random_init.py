@@ -135,6 +135,10 @@ def _fill(name, decl, seed, dtype, device, scales, int_high) -> torch.Tensor:
         kind, a, dt = "int", float(int_high), torch.int32
     elif decl.role == "norm_weight":
         kind, a, dt = "around_one", scales.norm_spread, dtype
+    elif decl.role == "norm_delta":                 # a norm weight stored around zero
+        kind, a, dt = "normal", scales.norm_spread, dtype
+    elif decl.role == "fraction":                   # a blend weight: 0.5 (1 + U(-1/4, 1/4))
+        kind, a, dt = "around_one", 0.25, dtype
     elif decl.role == "bias":
         kind, a, dt = "normal", scales.bias_std, dtype
     elif decl.role == "matrix":
@@ -143,16 +147,20 @@ def _fill(name, decl, seed, dtype, device, scales, int_high) -> torch.Tensor:
         raise QStreamError(QsError.INTERNAL, f"unknown tensor role '{decl.role}' for {name}")
     key = tensor_key(seed, name)
     shape = tuple(decl.shape)
+    if any(d < 0 for d in shape):
+        raise QStreamError(QsError.INVALID_MODEL, f"tensor '{name}' has a size that only a checkpoint gives: {shape}")
     n = math.prod(shape)
+    halve = decl.role == "fraction"
     if device.type == "cuda":
         from ..csrc import ops
-        out = torch.empty(shape, dtype=dt, device=device)
+        out = torch.empty(shape, dtype=torch.float32 if halve else dt, device=device)
         ops.random_fill(out, key, _KINDS[kind], a)
-        return out
+        return (out * 0.5).to(dt) if halve else out
     out = torch.empty(n, dtype=dt)
     for first in range(0, n, _HOST_CHUNK):          # bounded staging for very large tables
         m = min(_HOST_CHUNK, n - first)
-        out[first:first + m] = torch.from_numpy(host_values(key, kind, a, first, m)).to(dt)
+        vals = host_values(key, kind, a, first, m)
+        out[first:first + m] = torch.from_numpy(vals * np.float32(0.5) if halve else vals).to(dt)
     return out.reshape(shape)
 
 
