@@ -58,6 +58,7 @@ class DecodeGraph:
         # fixed parts of the metadata: every row is wanted, row i is sequence i
         for s in self.staging_np:
             s[self.offs[1]:self.offs[2]] = -1
+            s[self.offs[4]:self.offs[5]] = -1             # no sequence yet: the warm-up run before the capture touches no state
             s[self.offs[3]:self.offs[4]] = np.arange(rows)
             s[self.offs[5]:self.offs[6]] = np.arange(rows + 1)
             s[self.offs[7]:self.offs[8]] = -1
