@@ -37,10 +37,11 @@ decode_split_kernel(float* __restrict__ partial, const __nv_bfloat16* __restrict
                     const int32_t* __restrict__ page_table, int max_pages,
                     const int32_t* __restrict__ tok_slot, const int32_t* __restrict__ tok_pos,
                     int n_heads, int n_kv_heads, int dh, int gs_log2, float scale, int window, int max_splits,
-                    int32_t* __restrict__ status) {
+                    int32_t* __restrict__ status, int dv, float softcap) {
+    // dv: the values' head size (the keys' is dh); softcap c > 0: scores become c tanh(s / c)
     __shared__ float s_scores[WARPS][PAGE];
     __shared__ float s_m[WARPS], s_l[WARPS];
-    extern __shared__ float s_acc[];                 // [WARPS][dh]
+    extern __shared__ float s_acc[];                 // [WARPS][dv]
 
     const int split = blockIdx.x, head = blockIdx.y, t = blockIdx.z;
     const int slot = tok_slot[t];
@@ -56,7 +57,7 @@ decode_split_kernel(float* __restrict__ partial, const __nv_bfloat16* __restrict
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int GS = 1 << gs_log2, KPL = 32 >> gs_log2;
     const int chunk = lane & (GS - 1), sub = lane >> gs_log2;
-    const int n_chunks = dh >> 3;
+    const int n_chunks = dh >> 3, v_chunks = dv >> 3;
     const int kvh = head / (n_heads / n_kv_heads);
 
     // this lane's part of the query, in 32-bit
@@ -85,9 +86,9 @@ decode_split_kernel(float* __restrict__ partial, const __nv_bfloat16* __restrict
         if (page < 0) {
             if (lane == 0) atomicExch(status, 3);
         } else {
-            const size_t base = ((size_t)page * n_kv_heads + kvh) * PAGE * dh;
-            const __nv_bfloat16* kp = k_cache + base;
-            const __nv_bfloat16* vp = v_cache + base;
+            const size_t base = ((size_t)page * n_kv_heads + kvh) * PAGE;
+            const __nv_bfloat16* kp = k_cache + base * dh;
+            const __nv_bfloat16* vp = v_cache + base * dv;
             const int n_keys = min(PAGE, pos - key0 + 1);
             // scores of the page's keys, UNROLL warp loads in flight at a time
             for (int it0 = 0; it0 * KPL < n_keys; it0 += UNROLL) {
@@ -114,7 +115,9 @@ decode_split_kernel(float* __restrict__ partial, const __nv_bfloat16* __restrict
                         for (int j = 0; j < 8; ++j) dot = fmaf(qf[i][j], kf[j], dot);
                     }
                     for (int o = GS >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-                    if (chunk == 0 && kk < PAGE) s_scores[warp][kk] = (kk < n_keys && key0 + kk >= first) ? dot * scale : -INFINITY;
+                    float sc = dot * scale;
+                    if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);
+                    if (chunk == 0 && kk < PAGE) s_scores[warp][kk] = (kk < n_keys && key0 + kk >= first) ? sc : -INFINITY;
                 }
             }
             __syncwarp();
@@ -140,8 +143,8 @@ decode_split_kernel(float* __restrict__ partial, const __nv_bfloat16* __restrict
 #pragma unroll
                     for (int i = 0; i < NCH; ++i) {
                         const int c = chunk + i * GS;
-                        raw[u][i] = (kk < n_keys && c < n_chunks)
-                            ? __ldg(reinterpret_cast<const uint4*>(vp + (size_t)kk * dh + c * 8)) : make_uint4(0, 0, 0, 0);
+                        raw[u][i] = (kk < n_keys && c < v_chunks)
+                            ? __ldg(reinterpret_cast<const uint4*>(vp + (size_t)kk * dv + c * 8)) : make_uint4(0, 0, 0, 0);
                     }
                 }
 #pragma unroll
@@ -171,9 +174,9 @@ decode_split_kernel(float* __restrict__ partial, const __nv_bfloat16* __restrict
 #pragma unroll
         for (int i = 0; i < NCH; ++i) {
             const int c = chunk + i * GS;
-            if (c < n_chunks) {
+            if (c < v_chunks) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) s_acc[(size_t)warp * dh + c * 8 + j] = acc[i][j];
+                for (int j = 0; j < 8; ++j) s_acc[(size_t)warp * dv + c * 8 + j] = acc[i][j];
             }
         }
     }
@@ -181,12 +184,12 @@ decode_split_kernel(float* __restrict__ partial, const __nv_bfloat16* __restrict
     float M = -INFINITY;
 #pragma unroll
     for (int w = 0; w < WARPS; ++w) M = fmaxf(M, s_m[w]);
-    float* out = partial + (((size_t)t * n_heads + head) * max_splits + split) * (dh + 2);
-    for (int d = threadIdx.x; d < dh; d += blockDim.x) {
+    float* out = partial + (((size_t)t * n_heads + head) * max_splits + split) * (dv + 2);
+    for (int d = threadIdx.x; d < dv; d += blockDim.x) {
         float o = 0.f;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w)
-            if (s_m[w] != -INFINITY) o += s_acc[(size_t)w * dh + d] * expf(s_m[w] - M);
+            if (s_m[w] != -INFINITY) o += s_acc[(size_t)w * dv + d] * expf(s_m[w] - M);
         out[d] = o;
     }
     if (threadIdx.x == 0) {
@@ -194,15 +197,17 @@ decode_split_kernel(float* __restrict__ partial, const __nv_bfloat16* __restrict
 #pragma unroll
         for (int w = 0; w < WARPS; ++w)
             if (s_m[w] != -INFINITY) L += s_l[w] * expf(s_m[w] - M);
-        out[dh] = M;
-        out[dh + 1] = L;
+        out[dv] = M;
+        out[dv + 1] = L;
     }
 }
 
 // One block per (token, head): add the splits' partial results in ascending split order.
+// `dh` is the values' head size here.  `gate` (may be null): the row is multiplied by sigmoid(gate) on its way out.
 __global__ void decode_merge_kernel(__nv_bfloat16* __restrict__ out, size_t ldo, const float* __restrict__ partial,
                                     const int32_t* __restrict__ tok_slot, const int32_t* __restrict__ tok_pos,
-                                    int n_heads, int dh, int window, int max_splits) {
+                                    int n_heads, int dh, int window, int max_splits,
+                                    const __nv_bfloat16* __restrict__ gate, size_t ldg) {
     grid_dep_launch();
     const int head = blockIdx.x, t = blockIdx.y;
     __nv_bfloat16* o = out + (size_t)t * ldo + (size_t)head * dh;
@@ -251,7 +256,9 @@ __global__ void decode_merge_kernel(__nv_bfloat16* __restrict__ out, size_t ldo,
             for (int u = 0; u < AHEAD; ++u)
                 if (i0 + u < n && s_w[i0 + u] != 0.f) acc += v[u] * s_w[i0 + u];
         }
-        o[d] = __float2bfloat16_rn(acc * inv);
+        float r = acc * inv;
+        if (gate) r *= sigmoid_f32(__bfloat162float(gate[(size_t)t * ldg + (size_t)head * dh + d]));
+        o[d] = __float2bfloat16_rn(r);
     }
 }
 
@@ -268,13 +275,19 @@ QS_API long long qs_attention_decode_scratch(int T_tokens, int n_heads, int dh, 
 // `scratch`: float32, at least qs_attention_decode_scratch(...) elements; contents need no
 // initialisation.  A row whose position is negative or not below max_context rounded up to 256 sets
 // status 1 and gets zeros; `tok_slot` entries must be negative (padding) or rows of `page_table`.
-QS_API int qs_attention_decode(void* out, long long ldo, const void* q, long long ldq, const void* k_cache,
-                               const void* v_cache, const int32_t* page_table, int max_pages, int page_tokens,
-                               const int32_t* tok_slot, const int32_t* tok_pos, int T_tokens, int n_heads,
-                               int n_kv_heads, int dh, float scale, int window, int max_context,
-                               float* scratch, int32_t* status, cudaStream_t stream) {
+//
+// The general form: values with a head size `dv` of their own (out [T, n_heads * dv]; the scratch is sized by dv),
+// scores capped as softcap tanh(s / softcap) when softcap > 0, and an optional sigmoid gate [T, n_heads * dv]
+// (bfloat16, row stride ldg) on the output.
+QS_API int qs_attention_decode_ex(void* out, long long ldo, const void* q, long long ldq, const void* k_cache,
+                                  const void* v_cache, const int32_t* page_table, int max_pages, int page_tokens,
+                                  const int32_t* tok_slot, const int32_t* tok_pos, int T_tokens, int n_heads,
+                                  int n_kv_heads, int dh, float scale, int window, int max_context,
+                                  float* scratch, int32_t* status, int dv, float softcap, const void* gate,
+                                  long long ldg, cudaStream_t stream) {
     if (T_tokens == 0) return QS_OK;
     QS_REQUIRE(T_tokens > 0 && n_heads > 0 && n_kv_heads > 0 && dh > 0 && max_context > 0, "attention_decode: bad sizes");
+    QS_REQUIRE(dv > 0 && dv % 8 == 0 && dv <= 512, "attention_decode: value head size %d must be a multiple of 8, at most 512", dv);
     QS_REQUIRE(page_tokens == PAGE, "attention_decode: pages of %d tokens, the kernel is built for %d", page_tokens, PAGE);
     QS_REQUIRE(n_heads % n_kv_heads == 0, "attention_decode: %d query heads are no multiple of %d key heads", n_heads, n_kv_heads);
     QS_REQUIRE(dh % 8 == 0 && dh <= 512, "attention_decode: head size %d must be a multiple of 8, at most 512", dh);
@@ -282,7 +295,7 @@ QS_API int qs_attention_decode(void* out, long long ldo, const void* q, long lon
     QS_REQUIRE(T_tokens <= 65535 && n_heads <= 65535, "attention_decode: sizes exceed the grid");
     const int max_splits = (max_context + SPLIT - 1) / SPLIT;
     QS_REQUIRE(max_splits <= 4096, "attention_decode: a context of %d exceeds what the merge kernel holds (%d)", max_context, 4096 * SPLIT);
-    const int n_chunks = dh / 8;
+    const int n_chunks = (dh > dv ? dh : dv) / 8;       // a lane's chunk slots serve keys and values alike
     // Two 16-byte chunks per lane: half as many lanes share a key, so a score costs one shuffle step
     // less and a warp instruction covers twice the keys.  The grouping depends on the head size only
     // (it fixes the order of the sums); how many loads a lane keeps in flight does not change a bit
@@ -303,7 +316,7 @@ QS_API int qs_attention_decode(void* out, long long ldo, const void* q, long lon
         }
     }
     dim3 grid(max_splits, n_heads, T_tokens);
-    const size_t smem = (size_t)WARPS * dh * sizeof(float);
+    const size_t smem = (size_t)WARPS * dv * sizeof(float);
     static int sm_counts[64] = {0};                  // per device; a race only repeats the query
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
@@ -315,7 +328,8 @@ QS_API int qs_attention_decode(void* out, long long ldo, const void* q, long lon
     const bool few_ctas = (long long)max_splits * n_heads * T_tokens <= 2LL * sm_count;
 #define GO(NCH, UNROLL) decode_split_kernel<NCH, UNROLL><<<grid, WARPS * 32, smem, stream>>>( \
         scratch, (const __nv_bfloat16*)q, (size_t)ldq, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
-        page_table, max_pages, tok_slot, tok_pos, n_heads, n_kv_heads, dh, gs_log2, scale, window, max_splits, status)
+        page_table, max_pages, tok_slot, tok_pos, n_heads, n_kv_heads, dh, gs_log2, scale, window, max_splits, status, \
+        dv, softcap)
     if (nch == 1) GO(1, 8);
     else if (nch == 3) GO(3, 4);
     else if (nch == 5) GO(5, 2);
@@ -324,9 +338,20 @@ QS_API int qs_attention_decode(void* out, long long ldo, const void* q, long lon
 #undef GO
     int rc = qs_check_launch("attention_decode");
     if (rc != QS_OK) return rc;
-    decode_merge_kernel<<<dim3(n_heads, T_tokens), dh >= 128 ? 128 : 64, (size_t)3 * max_splits * sizeof(float), stream>>>(
-        (__nv_bfloat16*)out, (size_t)ldo, scratch, tok_slot, tok_pos, n_heads, dh, window, max_splits);
+    decode_merge_kernel<<<dim3(n_heads, T_tokens), dv >= 128 ? 128 : 64, (size_t)3 * max_splits * sizeof(float), stream>>>(
+        (__nv_bfloat16*)out, (size_t)ldo, scratch, tok_slot, tok_pos, n_heads, dv, window, max_splits,
+        (const __nv_bfloat16*)gate, (size_t)ldg);
     return qs_check_launch("attention_decode merge");
+}
+
+QS_API int qs_attention_decode(void* out, long long ldo, const void* q, long long ldq, const void* k_cache,
+                               const void* v_cache, const int32_t* page_table, int max_pages, int page_tokens,
+                               const int32_t* tok_slot, const int32_t* tok_pos, int T_tokens, int n_heads,
+                               int n_kv_heads, int dh, float scale, int window, int max_context,
+                               float* scratch, int32_t* status, cudaStream_t stream) {
+    return qs_attention_decode_ex(out, ldo, q, ldq, k_cache, v_cache, page_table, max_pages, page_tokens, tok_slot, tok_pos,
+                                  T_tokens, n_heads, n_kv_heads, dh, scale, window, max_context, scratch, status, dh, 0.f,
+                                  nullptr, 0, stream);
 }
 
 // ----------------------------------------------------------------------------- no allocation

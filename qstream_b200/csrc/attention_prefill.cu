@@ -68,7 +68,12 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                          const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, size_t ldo,
                          const TileInfo* __restrict__ tiles, const int32_t* __restrict__ page_table, int max_pages,
                          int n_heads, int n_kv_heads, int dh, float scale_log2, int window,
-                         int32_t* __restrict__ status) {
+                         int32_t* __restrict__ status, int dv, float cap_log2, float cap_k2,
+                         const __nv_bfloat16* __restrict__ gate, size_t ldg) {
+    // dh: head size of queries and keys, dv: of values and of the output (NKC covers the larger).  cap_log2 > 0:
+    // scores are capped, s <- c tanh(s scale / c), computed as cap_log2 (1 - 2 / (2^(s cap_k2) + 1)) in log2 units
+    // with cap_log2 = c log2(e) and cap_k2 = 2 log2(e) scale / c.  gate (may be null): the output row is multiplied
+    // by sigmoid(gate[row, head * dv + column]).
     constexpr int STAGES = kv_stages<NKC>();
     constexpr int KV_TILE = kv_tile_bytes<NKC>();
     constexpr uint32_t TMEM_COLS = NKC <= 2 ? 256 : 512;
@@ -132,10 +137,11 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     if (warp == 0) {
         // ------------------------------------------------------------------ producer
         if (elect_one()) {
-            mbar_expect_tx(q_full, q_bytes<NKC>());
+            const int n_kc = (dh + KC - 1) / KC, n_vc = (dv + KC - 1) / KC;      // 64-column tiles of keys / of values
+            mbar_expect_tx(q_full, BM * KC * 2 * n_kc);
 #pragma unroll
             for (int c = 0; c < NKC; ++c)
-                tma_load_2d(q_smem + c * BM * KC * 2, &map_q, q_full, head * dh + c * KC, tile.row_start);
+                if (c < n_kc) tma_load_2d(q_smem + c * BM * KC * 2, &map_q, q_full, head * dh + c * KC, tile.row_start);
             const int32_t* pages = page_table + (size_t)tile.slot * max_pages;
             auto tile_row = [&](int j) {
                 int page = pages[block_first + j];
@@ -147,9 +153,10 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 if (!mbar_wait(&k_empty[st], ((j / STAGES) & 1) ^ 1)) { atomicExch(status, 111); *aborted = 1; return false; }
                 const int row = tile_row(j);
                 uint8_t* k_tile = kv_smem + (size_t)st * 2 * KV_TILE;
-                mbar_expect_tx(&k_full[st], KV_TILE);
+                mbar_expect_tx(&k_full[st], BN * KC * 2 * n_kc);
 #pragma unroll
-                for (int c = 0; c < NKC; ++c) tma_load_2d(k_tile + c * BN * KC * 2, &map_k, &k_full[st], c * KC, row);
+                for (int c = 0; c < NKC; ++c)
+                    if (c < n_kc) tma_load_2d(k_tile + c * BN * KC * 2, &map_k, &k_full[st], c * KC, row);
                 return true;
             };
             auto load_v = [&](int j) -> bool {
@@ -157,9 +164,10 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 if (!mbar_wait(&v_empty[st], ((j / STAGES) & 1) ^ 1)) { atomicExch(status, 110); *aborted = 1; return false; }
                 const int row = tile_row(j);
                 uint8_t* v_tile = kv_smem + (size_t)st * 2 * KV_TILE + KV_TILE;
-                mbar_expect_tx(&v_full[st], KV_TILE);
+                mbar_expect_tx(&v_full[st], BN * KC * 2 * n_vc);
 #pragma unroll
-                for (int c = 0; c < NKC; ++c) tma_load_2d(v_tile + c * BN * KC * 2, &map_v, &v_full[st], c * KC, row);
+                for (int c = 0; c < NKC; ++c)
+                    if (c < n_vc) tma_load_2d(v_tile + c * BN * KC * 2, &map_v, &v_full[st], c * KC, row);
                 return true;
             };
             // in the order in which the slots come free: keys of block j + 1 (after Q K^T of block j + 1 - STAGES),
@@ -174,7 +182,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         // ------------------------------------------------------------------ MMA issuer
         if (elect_one()) {
             const uint32_t idesc_qk = idesc_bf16_f32(BM, BN);
-            const uint32_t idesc_pv = idesc_bf16_f32_b_mn(BM, dh);
+            const uint32_t idesc_pv = idesc_bf16_f32_b_mn(BM, dv);
             const int k_steps = (dh + 15) / 16;
             bool ok = mbar_wait(q_full, 0);
             if (!ok) { atomicExch(status, 112); *aborted = 1; }
@@ -242,6 +250,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
         float m = -INFINITY, l = 0.f;
         bool ok = true;
+        const float sl2 = cap_log2 > 0.f ? 1.0f : scale_log2;
         for (int j = 0; j < n_blocks; ++j) {
             if (ok && !mbar_wait(&s_full[j & 1], (j >> 1) & 1)) { atomicExch(status, 116); ok = false; }
             if (*aborted) ok = false;
@@ -251,6 +260,13 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             tmem_load_wait();
             const int key0 = (block_first + j) * BN + half * 32;
             const bool all_visible = key0 + 31 <= qpos && key0 >= lo;
+            if (cap_log2 > 0.f) {                    // the capped scores, already in log2 units (`sl2` is then 1)
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    const float e = fast_exp2(__uint_as_float(raw[c]) * cap_k2);
+                    raw[c] = __float_as_uint(cap_log2 * (1.0f - __fdividef(2.0f, e + 1.0f)));
+                }
+            }
             // raw scores stay in `raw`; masked ones become -inf.  The maximum is taken over four independent chains.
             if (!all_visible) {
 #pragma unroll
@@ -273,7 +289,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             xch[half * BM + r] = (uint16_t)(__float_as_uint(mine) >> 16);
             asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");      // the row's two threads sit in warps quad + 2 and quad + 6: a barrier of their own per quarter
             const float theirs = __uint_as_float((uint32_t)xch[(half ^ 1) * BM + r] << 16);
-            const float bmax = fmaxf(mine, theirs) * scale_log2;                      // scale_log2 > 0
+            const float bmax = fmaxf(mine, theirs) * sl2;                             // sl2 > 0
             // Two buffers of weights: this block's buffer is free once the P V of block j - 2 has completed
             // (a barrier per buffer), so these exponentials run under the P V of block j - 1.
             if (ok && j > 1 && !mbar_wait(&p_free[j & 1], ((j >> 1) - 1) & 1)) { atomicExch(status, 117); ok = false; }
@@ -285,7 +301,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     // O may only be touched between two P V products; the row's two threads take every other chunk
                     if (ok && !mbar_wait(pv_done, (j - 1) & 1)) { atomicExch(status, 119); ok = false; }
                     tc_fence_after_sync();
-                    for (int c = half; c * 32 < dh; c += 2) {
+                    for (int c = half; c * 32 < dv; c += 2) {
                         uint32_t o[32];
                         tmem_load_32x32(tmem_base + lane_base + O_COL + (uint32_t)(c * 32), o);
                         tmem_load_wait();
@@ -311,8 +327,8 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     for (int i = 0; i < 4; ++i) {
                         const int c = ch * 8 + 2 * i;
                         const float sa = __uint_as_float(raw[c]), sb = __uint_as_float(raw[c + 1]);
-                        const float a = neg_m == -INFINITY ? 0.f : fast_exp2(fmaf(sa, scale_log2, neg_m));
-                        const float b = neg_m == -INFINITY ? 0.f : fast_exp2(fmaf(sb, scale_log2, neg_m));
+                        const float a = neg_m == -INFINITY ? 0.f : fast_exp2(fmaf(sa, sl2, neg_m));
+                        const float b = neg_m == -INFINITY ? 0.f : fast_exp2(fmaf(sb, sl2, neg_m));
                         ps0 += a;
                         ps1 += b;
                         const __nv_bfloat162 pb = __floats2bfloat162_rn(a, b);
@@ -336,20 +352,31 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         if (ok && !*aborted) {
             tc_fence_after_sync();
             const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
-            __nv_bfloat16* orow = out + (size_t)(tile.row_start + r) * ldo + (size_t)head * dh;
-            for (int c = half; c * 32 < dh; c += 2) {
+            __nv_bfloat16* orow = out + (size_t)(tile.row_start + r) * ldo + (size_t)head * dv;
+            const __nv_bfloat16* grow = gate ? gate + (size_t)(tile.row_start + r) * ldg + (size_t)head * dv : nullptr;
+            for (int c = half; c * 32 < dv; c += 2) {
                 uint32_t o[32];
                 tmem_load_32x32(tmem_base + lane_base + O_COL + (uint32_t)(c * 32), o);
                 tmem_load_wait();
                 if (valid) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
-                        if (c * 32 + i < dh) {
+                        if (c * 32 + i < dv) {
                             uint32_t w[4];
+                            float g8[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f};
+                            if (grow) {
+                                const uint4 gr = *reinterpret_cast<const uint4*>(grow + c * 32 + i);
+                                const uint32_t gu[4] = {gr.x, gr.y, gr.z, gr.w};
+#pragma unroll
+                                for (int u = 0; u < 4; ++u) {
+                                    g8[2 * u] = sigmoid_f32(__uint_as_float(gu[u] << 16));
+                                    g8[2 * u + 1] = sigmoid_f32(__uint_as_float(gu[u] & 0xffff0000u));
+                                }
+                            }
 #pragma unroll
                             for (int u = 0; u < 4; ++u) {
-                                const __nv_bfloat162 pb = __floats2bfloat162_rn(__uint_as_float(o[i + 2 * u]) * inv,
-                                                                                 __uint_as_float(o[i + 2 * u + 1]) * inv);
+                                const __nv_bfloat162 pb = __floats2bfloat162_rn(__uint_as_float(o[i + 2 * u]) * inv * g8[2 * u],
+                                                                                 __uint_as_float(o[i + 2 * u + 1]) * inv * g8[2 * u + 1]);
                                 w[u] = *reinterpret_cast<const uint32_t*>(&pb);
                             }
                             *reinterpret_cast<uint4*>(orow + c * 32 + i) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -404,7 +431,8 @@ int make_map(CUtensorMap* out, const void* ptr, long long rows, long long cols, 
 template <int NKC>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, long long ldo,
            const TileInfo* tiles, int n_tiles, const int32_t* page_table, int max_pages, int n_heads, int n_kv_heads,
-           int dh, float scale_log2, int window, int32_t* status, cudaStream_t stream) {
+           int dh, float scale_log2, int window, int32_t* status, int dv, float cap_log2, float cap_k2, const void* gate,
+           long long ldg, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<NKC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -415,7 +443,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
     }
     attention_prefill_kernel<NKC><<<dim3(n_heads, n_tiles), THREADS, smem_bytes<NKC>(), stream>>>(
         mq, mk, mv, (__nv_bfloat16*)out, (size_t)ldo, tiles, page_table, max_pages, n_heads, n_kv_heads, dh,
-        scale_log2, window, status);
+        scale_log2, window, status, dv, cap_log2, cap_k2, (const __nv_bfloat16*)gate, (size_t)ldg);
     return qs_check_launch("attention_prefill");
 }
 
@@ -425,12 +453,20 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
 // tiles: device array of n_tiles x {row_start, n_rows (<= 128), position of the first row, slot}: the
 // query rows of each sequence cut into pieces of at most 128.  The cache entry is
 // [n_pages][n_kv_heads][64][dh].  Keys up to each row's own position must already be in the cache.
-QS_API int qs_attention_prefill(void* out, long long ldo, const void* q, long long ldq, int T_tokens,
-                                const void* k_cache, const void* v_cache, int n_pages,
-                                const int32_t* page_table, int max_pages, int page_tokens,
-                                const int32_t* tiles, int n_tiles, int n_heads, int n_kv_heads, int dh,
-                                float scale, int window, int32_t* status, cudaStream_t stream) {
+//
+// The general form: values with a head size `dv` of their own (V [n_pages][n_kv_heads][64][dv], out [T, n_heads * dv]),
+// scores capped as softcap tanh(s / softcap) when softcap > 0, and an optional sigmoid gate [T, n_heads * dv]
+// (bfloat16, row stride ldg, 16-byte aligned rows) on the output.
+QS_API int qs_attention_prefill_ex(void* out, long long ldo, const void* q, long long ldq, int T_tokens,
+                                   const void* k_cache, const void* v_cache, int n_pages,
+                                   const int32_t* page_table, int max_pages, int page_tokens,
+                                   const int32_t* tiles, int n_tiles, int n_heads, int n_kv_heads, int dh,
+                                   float scale, int window, int32_t* status, int dv, float softcap, const void* gate,
+                                   long long ldg, cudaStream_t stream) {
     if (n_tiles == 0 || T_tokens == 0) return QS_OK;
+    QS_REQUIRE(dv % 16 == 0 && dv >= 16 && dv <= 256, "attention_prefill: value head size %d must be a multiple of 16 up to 256", dv);
+    QS_REQUIRE(!gate || (ldg % 8 == 0 && ((uintptr_t)gate % 16) == 0), "attention_prefill: the gate's rows must be 16-byte aligned");
+    QS_REQUIRE(scale > 0.f && softcap >= 0.f, "attention_prefill: the scale must be positive and the cap not negative");
     QS_REQUIRE(T_tokens > 0 && n_tiles > 0 && n_heads > 0 && n_kv_heads > 0 && n_pages > 0, "attention_prefill: bad sizes");
     QS_REQUIRE(page_tokens == BN, "attention_prefill: pages of %d tokens, the kernel is built for %d", page_tokens, BN);
     QS_REQUIRE(n_heads % n_kv_heads == 0, "attention_prefill: %d query heads are no multiple of %d key heads", n_heads, n_kv_heads);
@@ -443,15 +479,27 @@ QS_API int qs_attention_prefill(void* out, long long ldo, const void* q, long lo
     if ((rc = make_map(&mq, q, T_tokens, (long long)n_heads * dh, ldq, BM)) != QS_OK) return rc;
     const long long kv_rows = (long long)n_pages * n_kv_heads * BN;
     if ((rc = make_map(&mk, k_cache, kv_rows, dh, dh, BN)) != QS_OK) return rc;
-    if ((rc = make_map(&mv, v_cache, kv_rows, dh, dh, BN)) != QS_OK) return rc;
-    const float scale_log2 = scale * 1.4426950408889634f;
+    if ((rc = make_map(&mv, v_cache, kv_rows, dv, dv, BN)) != QS_OK) return rc;
+    const float log2e = 1.4426950408889634f;
+    const float scale_log2 = scale * log2e;
+    const float cap_log2 = softcap > 0.f ? softcap * log2e : 0.f;
+    const float cap_k2 = softcap > 0.f ? 2.0f * log2e * scale / softcap : 0.f;
     const TileInfo* ti = reinterpret_cast<const TileInfo*>(tiles);
-    const int nkc = (dh + KC - 1) / KC;
+    const int nkc = ((dh > dv ? dh : dv) + KC - 1) / KC;
 #define GO(NKC) return launch<NKC>(mq, mk, mv, out, ldo, ti, n_tiles, page_table, max_pages, n_heads, n_kv_heads, dh, \
-                                   scale_log2, window, status, stream)
+                                   scale_log2, window, status, dv, cap_log2, cap_k2, gate, ldg, stream)
     if (nkc == 1) GO(1);
     if (nkc == 2) GO(2);
     if (nkc == 3) GO(3);
     GO(4);
 #undef GO
+}
+
+QS_API int qs_attention_prefill(void* out, long long ldo, const void* q, long long ldq, int T_tokens,
+                                const void* k_cache, const void* v_cache, int n_pages,
+                                const int32_t* page_table, int max_pages, int page_tokens,
+                                const int32_t* tiles, int n_tiles, int n_heads, int n_kv_heads, int dh,
+                                float scale, int window, int32_t* status, cudaStream_t stream) {
+    return qs_attention_prefill_ex(out, ldo, q, ldq, T_tokens, k_cache, v_cache, n_pages, page_table, max_pages, page_tokens,
+                                   tiles, n_tiles, n_heads, n_kv_heads, dh, scale, window, status, dh, 0.f, nullptr, 0, stream);
 }

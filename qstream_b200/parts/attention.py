@@ -133,24 +133,25 @@ class Attention(Mixer):
                            b.tok_slot, b.tok_pos, view.page_table, view.page_tokens, view.k, view.v,
                            step.status, settled=True,     # a step's slots, positions and pages arrive before its first kernel
                            v_head_dim=s.value_dim, v_first=v_first, v_mix=self.value_mix)
-        o = attend(q, s, step, view, out)
-        if s.gate:
-            o = ops.gated_group_norm(o, 0, None, qkv[:, qkv.shape[1] - s.n_heads * s.value_dim:], "sigmoid", 0.0, o.dtype)
-        return o
+        return attend(q, s, step, view, out, gate=qkv[:, qkv.shape[1] - s.n_heads * s.value_dim:] if s.gate else None)
 
 
-def attend(q, spec, step, view, out=None):
+def attend(q, spec, step, view, out=None, gate=None):
     """Pick the attention kernel for this step: decode and prefill have their own
-    bfloat16 kernels; the generic kernel takes every other case."""
+    bfloat16 kernels; the generic kernel takes every other case.  `gate` [T, heads * value_dim]: the result
+    times sigmoid(gate), in the bfloat16 kernels' last stage or by a kernel of its own."""
     b = step.batch
     if q.dtype == torch.bfloat16:
         from ..csrc import attention_bf16
-        done = attention_bf16.attend(q, spec, step, view, out)
+        done = attention_bf16.attend(q, spec, step, view, out, gate)
         if done is not None:
             return done
-    return ops.attention(q, spec.n_heads, spec.n_kv_heads, spec.head_dim, spec.scale, spec.window,
-                         b.tok_slot, b.tok_pos, view.page_table, view.page_tokens, view.k, view.v,
-                         step.status, out=out, v_head_dim=spec.value_dim, softcap=spec.softcap)
+    o = ops.attention(q, spec.n_heads, spec.n_kv_heads, spec.head_dim, spec.scale, spec.window,
+                      b.tok_slot, b.tok_pos, view.page_table, view.page_tokens, view.k, view.v,
+                      step.status, out=out, v_head_dim=spec.value_dim, softcap=spec.softcap)
+    if gate is not None:
+        o = ops.gated_group_norm(o, 0, None, gate, "sigmoid", 0.0, o.dtype)
+    return o
 
 
 register("mixer", "attention", Attention)

@@ -57,7 +57,19 @@ CONFIG_B = {
         attention_layer(6, 1, 10, 14, rot=(4, 1e6), softcap=12.0, mlp=DENSE(40)),
     ],
 }
-CONFIGS = {"A": CONFIG_A, "B": CONFIG_B}
+# C: head sizes that the bfloat16 tensor-core attention takes (multiples of 16), values narrower and wider than keys.
+CONFIG_C = {
+    "architecture": "Lutelorn", "vocab": 160, "width": 128, "norm": {"eps": 1e-5}, "residual_mult": 0.8,
+    "embedding": {"scale": 0.7, "bigram": {"buckets": 101, "mul_prev": 3, "mul_cur": 11}},
+    "layers": [
+        lightning_layer(32, 64, [0.9, 0.999], mlp=None),
+        attention_layer(4, 2, 64, 32, rot=(32, 10000.0), softcap=8.0, v_mix=True, mlp=DENSE(192)),
+        wkv_layer(2, 64, mlp=None),
+        attention_layer(2, 2, 48, 32, rot=(16, 1e5), softcap=0.0, v_mix=True, mlp=None),
+        attention_layer(2, 1, 16, 80, rot=None, softcap=20.0, scale=0.2, mlp=None),
+    ],
+}
+CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C}
 
 
 def make_weights(cfg: dict, seed: int, decay_rank: int = 5) -> dict[str, np.ndarray]:
@@ -118,7 +130,7 @@ def write_folder(folder, cfg: dict, weights: dict, dtype: str):
 
 def make_folder(tmp_path, which: str, dtype: str, seed: int = 0):
     cfg = CONFIGS[which]
-    return write_folder(tmp_path / f"lutelorn_{which}_{dtype}", cfg, make_weights(cfg, seed + (which == "B")), dtype), cfg
+    return write_folder(tmp_path / f"lutelorn_{which}_{dtype}", cfg, make_weights(cfg, seed + "ABC".index(which)), dtype), cfg
 
 
 def logits_error(got, ref):

@@ -11,7 +11,7 @@ from util import random_tokens
 
 pytestmark = pytest.mark.gpu
 
-CASES = [("A", "float32"), ("B", "float32"), ("A", "bfloat16"), ("B", "bfloat16")]
+CASES = [("A", "float32"), ("B", "float32"), ("A", "bfloat16"), ("B", "bfloat16"), ("C", "float32"), ("C", "bfloat16")]
 
 
 @pytest.fixture(scope="module")
@@ -116,7 +116,7 @@ def test_batches_of_unequal_requests_and_reused_slots(models, which, dtype):
     assert engine.cache.slots.n_free == engine.cache.slots.n_slots
 
 
-@pytest.mark.parametrize("which,dtype", [("A", "float32"), ("B", "bfloat16")])
+@pytest.mark.parametrize("which,dtype", [("A", "float32"), ("B", "bfloat16"), ("C", "bfloat16")])
 def test_long_decoding(models, which, dtype):
     """300 tokens one by one after a short prompt: across four page borders and the 256-token border at which
     the engine changes to another captured step; a second sequence runs along and ends early."""

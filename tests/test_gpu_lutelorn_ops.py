@@ -174,7 +174,7 @@ def test_states_of_a_batch_with_idle_and_padding_sequences():
 
 # --------------------------------------------------------------------------- attention
 
-def paged_attention(q, k, v, H, G, dk, dv, scale, softcap, dtype, page_order, rot=None, blend=None):
+def paged_attention(q, k, v, H, G, dk, dv, scale, softcap, dtype, page_order, rot=None, blend=None, fast=False, gate=None):
     """One sequence through rope_store and the attention kernel, its pages in `page_order`."""
     T = q.shape[0]
     n_pages = len(page_order)
@@ -194,6 +194,20 @@ def paged_attention(q, k, v, H, G, dk, dv, scale, softcap, dtype, page_order, ro
                    v_first=dev(blend[0], dtype) if blend else None, v_mix=blend[1] if blend else 0.0)
     out = ops.attention(qd, H, G, dk, scale, 0, slot, pos, table, 64, kc, vc, status, v_head_dim=dv, softcap=softcap)
     assert int(status.item()) == 0
+    if fast:
+        # the bfloat16 kernels of prompts (tensor cores, pieces of 128 and fewer rows) and of single tokens (keys
+        # split over CTAs), with a gate on the way out; they must agree with the generic kernel and the gate
+        from qstream_b200.csrc import attention_bf16
+        g = dev(gate, dtype)
+        pieces = [(a, min(128, T - a), a, 1) for a in range(0, T, 128)][::-1]
+        tiles = torch.tensor(pieces, dtype=torch.int32, device=DEV)
+        pre = attention_bf16.prefill(qd, H, G, dk, scale, 0, tiles, table, 64, kc, vc, status, v_head_dim=dv,
+                                     softcap=softcap, gate=g)
+        rows = [T - 1, 3, 64, 200]
+        dec = attention_bf16.decode(qd[rows].contiguous(), H, G, dk, scale, 0, i32([1] * 4), i32(rows), table, 64, kc, vc,
+                                    512, status, v_head_dim=dv, softcap=softcap, gate=g[rows].contiguous())
+        assert int(status.item()) == 0
+        return out, pre, dec, rows
     return out
 
 
@@ -222,6 +236,28 @@ def test_attention_with_a_far_key_that_wins(H, G, dk, dv, softcap, rot, dtype):
     got = paged_attention(q, k, v, H, G, dk, dv, scale, softcap, dtype, [4, 0, 5, 2, 1, 3], rot, (v_first, lam))
     close(got, ref, 2e-5 if dtype == torch.float32 else 2e-2, "blended values, pages out of order")
     # a model stores what the kernel stored: the plain reference on unrounded values is the bound above
+
+
+@pytest.mark.parametrize("H,G,dk,dv,softcap,rot", [(4, 2, 64, 32, 8.0, (32, 1e4)), (2, 1, 32, 64, 0.0, (16, 1e5)),
+                                                     (2, 2, 80, 80, 20.0, None), (3, 1, 128, 16, 5.0, (64, 1e6)),
+                                                     (2, 2, 16, 256, 0.0, None), (1, 1, 256, 48, 50.0, (256, 1e4))])
+def test_tensor_core_and_split_attention_kernels(H, G, dk, dv, softcap, rot):
+    rng = np.random.default_rng(dk + 7 * dv)
+    T = 330
+    q, k, v, gate = (rng.normal(0, 1, (T, n)) for n in (H * dk, G * dk, G * dv, H * dv))
+    if not rot:
+        k[3] = np.tile(q[200:, :dk].mean(0), G) * 3.0
+    q, k, v, gate = (dev(a, torch.bfloat16).float().cpu().numpy().astype(np.float64) for a in (q, k, v, gate))
+    scale = 1.3 * dk ** -0.5
+    qr, kr = q.reshape(T, H, dk), k.reshape(T, G, dk)
+    if rot:
+        qr, kr = P.rotate_pairs(qr, np.arange(T), *rot), P.rotate_pairs(kr, np.arange(T), *rot)
+    ref = P.capped_attention(qr, kr, v.reshape(T, G, dv), scale, softcap).reshape(T, H * dv)
+    out, pre, dec, rows = paged_attention(q, k, v, H, G, dk, dv, scale, softcap, torch.bfloat16, [2, 5, 0, 1, 4, 3], rot,
+                                          fast=True, gate=gate)
+    close(out, ref, 2e-2, "generic")
+    close(pre, ref * P.sigmoid(gate), 2e-2, "prompt kernel")
+    close(dec, (ref * P.sigmoid(gate))[rows], 2e-2, "single-token kernel")
 
 
 def test_softcap_limits_a_huge_score():

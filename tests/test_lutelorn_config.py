@@ -31,6 +31,8 @@ def test_every_size_comes_from_the_configuration():
     assert "l1.norm2" not in d and d["l2.mlp.gate"].shape == (80, 64)
     mixes = [b.mixer.value_mix for b in spec.layers if b.mixer.kind == "attention"]
     assert mixes == ["first", "blend", "blend"]
+    c = config_from_dict(CONFIGS["C"]).model_spec()         # a layer that does not ask for it blends nothing
+    assert [b.mixer.value_mix for b in c.layers if b.mixer.kind == "attention"] == ["first", "blend", None]
     assert spec.layers[5].mixer.position is None and spec.layers[5].mixer.scale == 0.3 and spec.layers[5].mixer.softcap == 0.0
     assert [b.residual_scale for b in spec.layers] == [0.6] * 7
     b = config_from_dict(CONFIGS["B"]).model_spec()
