@@ -47,7 +47,8 @@ _SIGNATURES = {
     "qs_keep_last_rows": ([c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_int, c_void_p], c_int),
     "qs_state_scan": ([c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int,
                        c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int,
-                       c_int, c_int, c_int, c_int, c_int, c_void_p], c_int),
+                       c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                       c_void_p], c_int),
     "qs_token_shift": ([c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_longlong,
                         c_void_p, c_void_p, c_int, c_int, c_int, c_void_p], c_int),
     "qs_argmax": ([c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p], c_int),
@@ -355,20 +356,31 @@ def keep_last_rows(dst: torch.Tensor, src: torch.Tensor, seq_start, seq_slot, n_
 
 
 def state_scan(mode: str, q, k, v, state, seq_start, seq_slot, n_seq, n_heads, key_dim, value_dim, head_decay=None,
-               decay_logits=None, bonus=None, in_activation=None) -> torch.Tensor:
+               decay_logits=None, bonus=None, in_activation=None, chunks=None) -> torch.Tensor:
     """Walk each sequence's tokens of this step through a per-head matrix state (float32 [slots, heads, value_dim,
     key_dim], updated in place); returns o [T, heads * value_dim] in float32.
     mode "decay": S <- decay_h S + k v^T, o = S^T q.  mode "wkv": o = (S + diag(bonus) k v^T)^T q, then
-    S <- diag(exp(-exp(decay_logits))) S + k v^T."""
+    S <- diag(exp(-exp(decay_logits))) S + k v^T.
+    `chunks` = (chunk_start, chunk_ids, seq_chunk, n_chunks), int32 device tensors: every sequence of the step cut
+    into consecutive chunks (rows chunk_start[c] .. chunk_start[c + 1] of the packed batch; sequence s owns chunks
+    seq_chunk[s] .. seq_chunk[s + 1]; chunk_ids = 0 .. n_chunks - 1).  The chunks then run side by side and a
+    prefix over each sequence's chunks joins them; the result equals the walk in order up to 32-bit rounding."""
     T = q.shape[0]
     o = torch.empty((T, n_heads * value_dim), dtype=torch.float32, device=q.device)
     if state.dtype != torch.float32 or state.stride(-1) != 1:
         raise QStreamError(QsError.INVALID_INPUT, "state_scan: the state must be float32")
+    chunk_start = chunk_ids = seq_chunk = chunk_state = chunk_decay = None
+    n_chunks = 0
+    if chunks is not None:
+        chunk_start, chunk_ids, seq_chunk, n_chunks = chunks
+        chunk_state = torch.empty((n_chunks, n_heads * value_dim * key_dim), dtype=torch.float32, device=q.device)
+        chunk_decay = torch.empty((n_chunks, n_heads * key_dim), dtype=torch.float32, device=q.device)
     check(library().qs_state_scan(
         1 if mode == "wkv" else 0, ptr(o), o.stride(0), ptr(q), q.stride(0), ptr(k), k.stride(0), ptr(v), v.stride(0),
         dtype_code(q), ptr(decay_logits), decay_logits.stride(0) if decay_logits is not None else 0, ptr(head_decay),
         ptr(bonus), _code(bonus), ptr(state), state.stride(0), _int32(seq_start, "seq_start"),
-        _int32(seq_slot, "seq_slot"), int(n_seq), T, n_heads, key_dim, value_dim, ACTIVATIONS[in_activation], stream()))
+        _int32(seq_slot, "seq_slot"), int(n_seq), T, n_heads, key_dim, value_dim, ACTIVATIONS[in_activation],
+        ptr(chunk_start), ptr(chunk_ids), int(n_chunks), ptr(seq_chunk), ptr(chunk_state), ptr(chunk_decay), stream()))
     return o
 
 

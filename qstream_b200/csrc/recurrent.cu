@@ -18,7 +18,18 @@ namespace {
 constexpr int RK = 32;              // key rows per thread
 constexpr int TILE = 8;             // tokens staged in shared memory at a time
 
-template <typename TI, bool WKV>
+// Which rows a thread owns: groups of four consecutive rows, dealt to the KS threads of a column in turn, so that
+// the threads' 16-byte accesses to a column of the state and to a token's q and k lie side by side.
+__device__ __forceinline__ int row_of(int ks, int ks_log2, int r) { return 4 * (ks + ((r >> 2) << ks_log2)) + (r & 3); }
+
+// PHASE 0: a sequence's tokens in order from the state its slot holds, which is written back at the end.
+// A long prompt is cut into chunks that run side by side, in three steps whose sums are 32-bit throughout:
+// PHASE 1: every chunk by itself from a zero state (its own part of every o, and the state it adds); then
+//          `chunk_prefix_kernel` walks each sequence's chunks, replacing each chunk's added state by the state
+//          the chunk starts from and leaving the sequence's last state in its slot;
+// PHASE 3: every chunk adds to its tokens' o what the state it started from contributes, decayed up to each token.
+// For phases 1 and 3 a "sequence" of the kernel is a chunk and its "slot" the chunk's place in the scratch.
+template <typename TI, bool WKV, int PHASE>
 __global__ void __launch_bounds__(256)
 state_scan_kernel(float* __restrict__ o, size_t ldo,
                   const TI* __restrict__ q, size_t ldq, const TI* __restrict__ k, size_t ldk,
@@ -26,77 +37,111 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
                   const float* __restrict__ head_decay, const void* __restrict__ bonus, int bonus_dtype,
                   float* __restrict__ state, size_t slot_stride,
                   const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot, int n_seq, int T_rows,
-                  int H, int dk, int dv, int ks_log2, int cols, int in_act) {
+                  int H, int dk, int dv, int ks_log2, int cols, int in_act, int vec) {
     extern __shared__ float smem[];
     const int KS = 1 << ks_log2, dkp = KS * RK;
     float* sq = smem;                                   // [TILE][dkp]
     float* sk = sq + TILE * dkp;                        // [TILE][dkp]
     float* sw = sk + TILE * dkp;                        // [TILE][dkp]   (WKV only)
     float* sv = sw + (WKV ? TILE * dkp : 0);            // [TILE][cols]
+    float* carry = sv + TILE * cols;                    // [dkp]         (PHASE 3: the decay from the chunk's start on)
     grid_dep_launch();
     grid_dep_wait();
     const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * cols;
     const int n_cols = min(cols, dv - col0);
     const int tid = threadIdx.x;
     // rows of the packed batch beyond the last sequence belong to nobody: give them a defined value
-    if (s == 0) {
+    if (PHASE != 3 && s == 0) {
         for (int t = seq_start[n_seq]; t < T_rows; ++t)
             for (int c = tid; c < n_cols; c += blockDim.x) o[(size_t)t * ldo + h * dv + col0 + c] = 0.f;
     }
     const int slot = seq_slot[s];
     const int t0 = seq_start[s], t1 = seq_start[s + 1];
     if (slot < 0) {
-        for (int t = t0; t < t1; ++t)
-            for (int c = tid; c < n_cols; c += blockDim.x) o[(size_t)t * ldo + h * dv + col0 + c] = 0.f;
+        if (PHASE != 3)
+            for (int t = t0; t < t1; ++t)
+                for (int c = tid; c < n_cols; c += blockDim.x) o[(size_t)t * ldo + h * dv + col0 + c] = 0.f;
         return;
     }
     if (t1 <= t0) return;
     const int col = tid >> ks_log2, ks = tid & (KS - 1);
     const bool owner = col < n_cols;
-    const int i0 = ks * RK;
     float* scol = state + (size_t)slot * slot_stride + ((size_t)h * dv + col0 + (owner ? col : 0)) * dk;
 
     float S[RK], u[RK];
 #pragma unroll
-    for (int r = 0; r < RK; ++r) {
-        S[r] = (owner && i0 + r < dk) ? scol[i0 + r] : 0.f;
-        u[r] = (WKV && i0 + r < dk) ? load_as_f32(bonus, bonus_dtype, (size_t)h * dk + i0 + r) : 0.f;
+    for (int r4 = 0; r4 < RK / 4; ++r4) {
+        const int i = row_of(ks, ks_log2, 4 * r4);
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (PHASE != 1 && owner) {
+            if (vec) { if (i < dk) x = *reinterpret_cast<const float4*>(scol + i); }
+            else {
+                if (i < dk) x.x = scol[i];
+                if (i + 1 < dk) x.y = scol[i + 1];
+                if (i + 2 < dk) x.z = scol[i + 2];
+                if (i + 3 < dk) x.w = scol[i + 3];
+            }
+        }
+        S[4 * r4] = x.x; S[4 * r4 + 1] = x.y; S[4 * r4 + 2] = x.z; S[4 * r4 + 3] = x.w;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            u[4 * r4 + j] = (WKV && PHASE != 3 && i + j < dk) ? load_as_f32(bonus, bonus_dtype, (size_t)h * dk + i + j) : 0.f;
     }
     const float decay = WKV ? 0.f : head_decay[h];
+    if (PHASE == 3)
+        for (int i = tid; i < dkp; i += blockDim.x) carry[i] = 1.0f;
 
     for (int base = t0; base < t1; base += TILE) {
         const int nt = min(TILE, t1 - base);
         __syncthreads();
-        for (int e = tid; e < nt * dkp; e += blockDim.x) {
-            const int tt = e / dkp, i = e - tt * dkp;
-            const size_t row = (size_t)(base + tt);
-            float qv = 0.f, kv = 0.f, wv = 0.f;
-            if (i < dk) {
-                qv = apply_activation(to_f32(q[row * ldq + h * dk + i]), in_act);
-                kv = apply_activation(to_f32(k[row * ldk + h * dk + i]), in_act);
-                if (WKV) wv = expf(-expf(dlog[row * ldd + h * dk + i]));
+        // a thread stages one key row of the tile's tokens, in order: in PHASE 3 the row's decay since the chunk's
+        // start runs along and q arrives multiplied by it
+        for (int i = tid; i < dkp; i += blockDim.x) {
+            float run = PHASE == 3 ? carry[i] : 1.0f;
+            for (int tt = 0; tt < nt; ++tt) {
+                const size_t row = (size_t)(base + tt);
+                float qv = 0.f, kv = 0.f, wv = 0.f;
+                if (i < dk) {
+                    qv = apply_activation(to_f32(q[row * ldq + h * dk + i]), in_act);
+                    if (PHASE != 3) kv = apply_activation(to_f32(k[row * ldk + h * dk + i]), in_act);
+                    if (WKV) wv = expf(-expf(dlog[row * ldd + h * dk + i]));
+                }
+                if (PHASE == 3) {
+                    if (WKV) { qv *= run; run *= wv; }
+                    else { run *= decay; qv *= run; }
+                } else {
+                    sk[tt * dkp + i] = kv;
+                    if (WKV) sw[tt * dkp + i] = wv;
+                }
+                sq[tt * dkp + i] = qv;
             }
-            sq[e] = qv;
-            sk[e] = kv;
-            if (WKV) sw[e] = wv;
+            if (PHASE == 3) carry[i] = run;
         }
-        for (int e = tid; e < nt * cols; e += blockDim.x) {
-            const int tt = e / cols, c = e - tt * cols;
-            sv[e] = c < n_cols ? apply_activation(to_f32(v[(size_t)(base + tt) * ldv + h * dv + col0 + c]), in_act) : 0.f;
-        }
+        if (PHASE != 3)
+            for (int e = tid; e < nt * cols; e += blockDim.x) {
+                const int tt = e / cols, c = e - tt * cols;
+                sv[e] = c < n_cols ? apply_activation(to_f32(v[(size_t)(base + tt) * ldv + h * dv + col0 + c]), in_act) : 0.f;
+            }
         __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {
-            const float vj = sv[tt * cols + (owner ? col : 0)];
-            const float4* q4 = reinterpret_cast<const float4*>(sq + tt * dkp + i0);
-            const float4* k4 = reinterpret_cast<const float4*>(sk + tt * dkp + i0);
-            const float4* w4 = reinterpret_cast<const float4*>(sw + tt * dkp + i0);
+            const float vj = PHASE == 3 ? 0.f : sv[tt * cols + (owner ? col : 0)];
+            const float4* q4 = reinterpret_cast<const float4*>(sq + tt * dkp) + ks;
+            const float4* k4 = reinterpret_cast<const float4*>(sk + tt * dkp) + ks;
+            const float4* w4 = reinterpret_cast<const float4*>(sw + tt * dkp) + ks;
             float acc = 0.f;
 #pragma unroll
             for (int r4 = 0; r4 < RK / 4; ++r4) {
-                const float4 qq = q4[r4], kk = k4[r4];
-                const float qa[4] = {qq.x, qq.y, qq.z, qq.w}, ka[4] = {kk.x, kk.y, kk.z, kk.w};
+                const float4 qq = q4[r4 << ks_log2];
+                const float qa[4] = {qq.x, qq.y, qq.z, qq.w};
+                if (PHASE == 3) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc = fmaf(qa[j], S[r4 * 4 + j], acc);
+                    continue;
+                }
+                const float4 kk = k4[r4 << ks_log2];
+                const float ka[4] = {kk.x, kk.y, kk.z, kk.w};
                 float wa[4] = {0.f, 0.f, 0.f, 0.f};
-                if (WKV) { const float4 ww = w4[r4]; wa[0] = ww.x; wa[1] = ww.y; wa[2] = ww.z; wa[3] = ww.w; }
+                if (WKV) { const float4 ww = w4[r4 << ks_log2]; wa[0] = ww.x; wa[1] = ww.y; wa[2] = ww.z; wa[3] = ww.w; }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int r = r4 * 4 + j;
@@ -111,13 +156,68 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
                 }
             }
             for (int off = KS >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-            if (owner && ks == 0) o[(size_t)(base + tt) * ldo + h * dv + col0 + col] = acc;
+            if (owner && ks == 0) {
+                float* dst = o + (size_t)(base + tt) * ldo + h * dv + col0 + col;
+                *dst = PHASE == 3 ? *dst + acc : acc;
+            }
         }
     }
-    if (owner) {
+    if (PHASE != 3 && owner) {
 #pragma unroll
-        for (int r = 0; r < RK; ++r)
-            if (i0 + r < dk) scol[i0 + r] = S[r];
+        for (int r4 = 0; r4 < RK / 4; ++r4) {
+            const int i = row_of(ks, ks_log2, 4 * r4);
+            if (vec) { if (i < dk) *reinterpret_cast<float4*>(scol + i) = make_float4(S[4 * r4], S[4 * r4 + 1], S[4 * r4 + 2], S[4 * r4 + 3]); }
+            else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (i + j < dk) scol[i + j] = S[4 * r4 + j];
+            }
+        }
+    }
+}
+
+// The decay of every key channel over a whole chunk: exp(-sum_t exp(dlog[t])) (the product of the tokens' decays),
+// or decay_h ^ tokens for a fixed decay per head.  chunk_decay [chunks][H * dk].
+__global__ void chunk_decay_kernel(float* __restrict__ chunk_decay, const float* __restrict__ dlog, size_t ldd,
+                                   const float* __restrict__ head_decay, const int32_t* __restrict__ chunk_start,
+                                   int n, int dk) {
+    const int c = blockIdx.x;
+    const int t0 = chunk_start[c], t1 = chunk_start[c + 1];
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < n; i += gridDim.y * blockDim.x) {
+        float a;
+        if (dlog) {
+            float sum = 0.f;
+            for (int t = t0; t < t1; ++t) sum += expf(dlog[(size_t)t * ldd + i]);
+            a = expf(-sum);
+        } else {
+            a = 1.0f;
+            const float d = head_decay[i / dk];
+            for (int t = t0; t < t1; ++t) a *= d;
+        }
+        chunk_decay[(size_t)c * n + i] = a;
+    }
+}
+
+// Walk each sequence's chunks in order: chunk_state[c] (what chunk c adds, from PHASE 1) becomes the state that
+// chunk c starts from; the state after the last chunk goes to the sequence's slot.  One thread per state element
+// [h][j][i]; the decay belongs to (h, i).
+__global__ void chunk_prefix_kernel(float* __restrict__ chunk_state, const float* __restrict__ chunk_decay,
+                                    float* __restrict__ state, size_t slot_stride, const int32_t* __restrict__ seq_chunk,
+                                    const int32_t* __restrict__ seq_slot, int H, int dk, int dv) {
+    const int s = blockIdx.x;
+    const int slot = seq_slot[s];
+    const int c0 = seq_chunk[s], c1 = seq_chunk[s + 1];
+    if (slot < 0 || c1 <= c0) return;
+    const size_t n = (size_t)H * dv * dk;
+    for (size_t e = (size_t)blockIdx.y * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.y * blockDim.x) {
+        const int i = (int)(e % dk), h = (int)(e / ((size_t)dv * dk));
+        float S = state[(size_t)slot * slot_stride + e];
+        for (int c = c0; c < c1; ++c) {
+            const float added = chunk_state[(size_t)c * n + e];
+            chunk_state[(size_t)c * n + e] = S;
+            S = fmaf(chunk_decay[(size_t)c * H * dk + (size_t)h * dk + i], S, added);
+        }
+        state[(size_t)slot * slot_stride + e] = S;
     }
 }
 
@@ -146,10 +246,10 @@ __global__ void token_shift_kernel(T* __restrict__ out, size_t ldo, size_t mix_s
 }
 
 template <typename TI>
-int launch_scan(bool wkv, float* o, long long ldo, const void* q, long long ldq, const void* k, long long ldk, const void* v,
-                long long ldv, const float* dlog, long long ldd, const float* head_decay, const void* bonus, int bonus_dtype,
-                float* state, long long slot_stride, const int32_t* seq_start, const int32_t* seq_slot, int n_seq, int T_rows,
-                int H, int dk, int dv, int in_act, cudaStream_t stream) {
+int launch_scan(bool wkv, int phase, float* o, long long ldo, const void* q, long long ldq, const void* k, long long ldk,
+                const void* v, long long ldv, const float* dlog, long long ldd, const float* head_decay, const void* bonus,
+                int bonus_dtype, float* state, long long slot_stride, const int32_t* seq_start, const int32_t* seq_slot,
+                int n_seq, int T_rows, int H, int dk, int dv, int in_act, cudaStream_t stream) {
     int ks_log2 = 0;
     while ((RK << ks_log2) < dk) ++ks_log2;
     const int KS = 1 << ks_log2;
@@ -159,19 +259,16 @@ int launch_scan(bool wkv, float* o, long long ldo, const void* q, long long ldq,
     while (cols > 8 && (long long)n_seq * H * ((dv + cols - 1) / cols) < 148 && cols * KS > 64) cols >>= 1;
     const int threads = ((cols * KS + 31) / 32) * 32;
     const int dkp = KS * RK;
-    const size_t smem = (size_t)TILE * ((wkv ? 3 : 2) * dkp + cols) * sizeof(float);
+    const size_t smem = ((size_t)TILE * ((wkv ? 3 : 2) * dkp + cols) + dkp) * sizeof(float);
+    const int vec = dk % 4 == 0 && slot_stride % 4 == 0 && ((uintptr_t)state % 16) == 0;
     dim3 grid(n_seq, H, (dv + cols - 1) / cols);
     cudaError_t e;
-    if (wkv)
-        e = qs_launch_dependent(state_scan_kernel<TI, true>, grid, dim3(threads), smem, stream, o, (size_t)ldo, (const TI*)q,
-                                (size_t)ldq, (const TI*)k, (size_t)ldk, (const TI*)v, (size_t)ldv, dlog, (size_t)ldd, head_decay,
-                                bonus, bonus_dtype, state, (size_t)slot_stride, seq_start, seq_slot, n_seq, T_rows, H, dk, dv,
-                                ks_log2, cols, in_act);
-    else
-        e = qs_launch_dependent(state_scan_kernel<TI, false>, grid, dim3(threads), smem, stream, o, (size_t)ldo, (const TI*)q,
-                                (size_t)ldq, (const TI*)k, (size_t)ldk, (const TI*)v, (size_t)ldv, dlog, (size_t)ldd, head_decay,
-                                bonus, bonus_dtype, state, (size_t)slot_stride, seq_start, seq_slot, n_seq, T_rows, H, dk, dv,
-                                ks_log2, cols, in_act);
+#define GO(WKV, PHASE) e = qs_launch_dependent(state_scan_kernel<TI, WKV, PHASE>, grid, dim3(threads), smem, stream, o, (size_t)ldo, \
+        (const TI*)q, (size_t)ldq, (const TI*)k, (size_t)ldk, (const TI*)v, (size_t)ldv, dlog, (size_t)ldd, head_decay, bonus, \
+        bonus_dtype, state, (size_t)slot_stride, seq_start, seq_slot, n_seq, T_rows, H, dk, dv, ks_log2, cols, in_act, vec)
+    if (wkv) { if (phase == 0) GO(true, 0); else if (phase == 1) GO(true, 1); else GO(true, 3); }
+    else { if (phase == 0) GO(false, 0); else if (phase == 1) GO(false, 1); else GO(false, 3); }
+#undef GO
     if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "state_scan: %s", cudaGetErrorString(e));
     return qs_check_launch("state_scan");
 }
@@ -182,23 +279,45 @@ int launch_scan(bool wkv, float* o, long long ldo, const void* q, long long ldq,
 // key channel (`dlog` [T, H * dk] float32) and the bonus `bonus` [H, dk] for the current token.
 // q, k [T, H * dk] and v [T, H * dv] of type `dtype`, with `in_act` applied on the way in; o [T, H * dv] float32;
 // state [slots][H][dv][dk] float32 with `slot_stride` floats between slots.
+//
+// With `chunk_start` (device, n_chunks + 1 rows of the packed batch; every sequence of the step cut into consecutive
+// chunks, in packed order) the prompt's chunks run side by side: `seq_chunk` (n_seq + 1) names each sequence's
+// chunks, `chunk_state` ([n_chunks][H][dv][dk]) and `chunk_decay` ([n_chunks][H * dk]) are scratch, `chunk_ids`
+// holds 0 .. n_chunks - 1.  The result equals the walk in order up to the rounding of 32-bit sums.
 QS_API int qs_state_scan(int mode, float* o, long long ldo, const void* q, long long ldq, const void* k, long long ldk,
                          const void* v, long long ldv, int dtype, const float* dlog, long long ldd, const float* head_decay,
                          const void* bonus, int bonus_dtype, float* state, long long slot_stride, const int32_t* seq_start,
                          const int32_t* seq_slot, int n_seq, int T_rows, int H, int dk, int dv, int in_act,
-                         cudaStream_t stream) {
+                         const int32_t* chunk_start, const int32_t* chunk_ids, int n_chunks, const int32_t* seq_chunk,
+                         float* chunk_state, float* chunk_decay, cudaStream_t stream) {
     if (n_seq == 0 || T_rows == 0) return QS_OK;
     QS_REQUIRE(n_seq > 0 && T_rows > 0 && H > 0 && dk > 0 && dv > 0, "state_scan: bad sizes");
     QS_REQUIRE(dk <= 8 * RK, "state_scan: %d key channels per head above %d", dk, 8 * RK);
     QS_REQUIRE(H <= 65535, "state_scan: %d heads exceed the grid", H);
     QS_REQUIRE(mode == 0 ? head_decay != nullptr : (mode == 1 && dlog && bonus), "state_scan: mode %d lacks its operands", mode);
-    if (dtype == QS_F32)
-        return launch_scan<float>(mode == 1, o, ldo, q, ldq, k, ldk, v, ldv, dlog, ldd, head_decay, bonus, bonus_dtype, state,
-                                  slot_stride, seq_start, seq_slot, n_seq, T_rows, H, dk, dv, in_act, stream);
-    if (dtype == QS_BF16)
-        return launch_scan<__nv_bfloat16>(mode == 1, o, ldo, q, ldq, k, ldk, v, ldv, dlog, ldd, head_decay, bonus, bonus_dtype,
-                                          state, slot_stride, seq_start, seq_slot, n_seq, T_rows, H, dk, dv, in_act, stream);
-    return qs_fail(QS_ERR_INVALID_INPUT, "state_scan: unknown dtype %d", dtype);
+    QS_REQUIRE(dtype == QS_F32 || dtype == QS_BF16, "state_scan: unknown dtype %d", dtype);
+    const bool wkv = mode == 1;
+#define SCAN(PHASE, STATE, STRIDE, STARTS, SLOTS, N) (dtype == QS_F32 \
+        ? launch_scan<float>(wkv, PHASE, o, ldo, q, ldq, k, ldk, v, ldv, dlog, ldd, head_decay, bonus, bonus_dtype, STATE, STRIDE, \
+                             STARTS, SLOTS, N, T_rows, H, dk, dv, in_act, stream) \
+        : launch_scan<__nv_bfloat16>(wkv, PHASE, o, ldo, q, ldq, k, ldk, v, ldv, dlog, ldd, head_decay, bonus, bonus_dtype, STATE, \
+                                     STRIDE, STARTS, SLOTS, N, T_rows, H, dk, dv, in_act, stream))
+    if (!chunk_start) return SCAN(0, state, slot_stride, seq_start, seq_slot, n_seq);
+    QS_REQUIRE(n_chunks > 0 && chunk_ids && seq_chunk && chunk_state && chunk_decay, "state_scan: chunks without their scratch");
+    const long long per_chunk = (long long)H * dv * dk;
+    int rc = SCAN(1, chunk_state, per_chunk, chunk_start, chunk_ids, n_chunks);
+    if (rc != QS_OK) return rc;
+    const int n = H * dk;
+    chunk_decay_kernel<<<dim3(n_chunks, (n + 127) / 128), 128, 0, stream>>>(chunk_decay, wkv ? dlog : nullptr, (size_t)ldd,
+                                                                            head_decay, chunk_start, n, dk);
+    if ((rc = qs_check_launch("state_scan chunk decay")) != QS_OK) return rc;
+    int by = (int)((per_chunk + 255) / 256);
+    if (by > 1024) by = 1024;
+    chunk_prefix_kernel<<<dim3(n_seq, by), 256, 0, stream>>>(chunk_state, chunk_decay, state, (size_t)slot_stride, seq_chunk,
+                                                              seq_slot, H, dk, dv);
+    if ((rc = qs_check_launch("state_scan chunk prefix")) != QS_OK) return rc;
+    return SCAN(3, chunk_state, per_chunk, chunk_start, chunk_ids, n_chunks);
+#undef SCAN
 }
 
 QS_API int qs_token_shift(void* out, long long ldo, long long mix_stride, const void* h, long long ldh, int dtype,

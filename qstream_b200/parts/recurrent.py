@@ -10,8 +10,9 @@ two-matrix bottleneck whose output d gives the decay w = exp(-exp(d + w0)) per t
 each head's o is divided by its root mean square, then weight, silu gate, W_o.
 
 Both keep S in 32-bit per sequence (`StateNeed`), zero when a slot is taken, read at the start of a step and
-written at its end by one kernel that walks a sequence's tokens in order (csrc/recurrent.cu); prompts and single
-tokens take the same path.  The projections are matrix products in the engine's type; decays, the recurrence,
+written at its end by one kernel that walks a sequence's tokens in order (csrc/recurrent.cu); single tokens and
+short prompts take that path, a long prompt is cut into chunks that run side by side and are joined by a prefix
+over the chunks' states.  The projections are matrix products in the engine's type; decays, the recurrence,
 its output and the norms are 32-bit.
 """
 from __future__ import annotations
@@ -24,6 +25,33 @@ from ..errors import QsError, QStreamError
 from ..weights.loader import TensorDecl
 from .base import Mixer, register
 from .linear import linear
+
+
+CHUNK_TOKENS = 64            # a long prompt is cut into chunks of this many tokens that run side by side
+CHUNKED_FROM = 256           # the longest sequence of a step from which that pays
+
+
+def scan_chunks(batch, device):
+    """The step's sequences cut into chunks for `ops.state_scan`, or None where the walk in order serves: single
+    tokens, short prompts, and captured steps (whose host lists are not the step's)."""
+    cached = getattr(batch, "_scan_chunks", False)
+    if cached is not False:
+        return cached
+    out = None
+    n_new = batch.new_tokens
+    if n_new and len(n_new) == batch.n_seq and sum(n_new) == batch.n_tokens and max(n_new) >= CHUNKED_FROM:
+        import numpy as np
+        starts, owners, row = [0], [0], 0
+        for n in n_new:
+            starts += [row + min(n, a + CHUNK_TOKENS) for a in range(0, n, CHUNK_TOKENS)]
+            row += n
+            owners.append(len(starts) - 1)
+        n_chunks = len(starts) - 1
+        host = torch.from_numpy(np.concatenate([starts, np.arange(n_chunks), owners]).astype(np.int32))
+        dev = host.pin_memory().to(device, non_blocking=True) if device.type == "cuda" else host
+        out = (dev[:n_chunks + 1], dev[n_chunks + 1:2 * n_chunks + 1], dev[2 * n_chunks + 1:], n_chunks)
+    batch._scan_chunks = out
+    return out
 
 
 class DecayAttention(Mixer):
@@ -53,7 +81,7 @@ class DecayAttention(Mixer):
         p = linear(h, self.w_in)
         o = ops.state_scan("decay", p[:, :hk], p[:, hk:2 * hk], p[:, 2 * hk:2 * hk + hv], step.state(cache_id),
                            b.seq_start, b.seq_slot, b.n_seq, s.n_heads, s.key_dim, s.value_dim,
-                           head_decay=self.decay, in_activation=s.activation)
+                           head_decay=self.decay, in_activation=s.activation, chunks=scan_chunks(b, h.device))
         y = ops.gated_group_norm(o, hv, self.norm, p[:, 2 * hk + hv:], "sigmoid", s.eps, h.dtype)
         return linear(y, self.w_out, None, residuals=residuals, out_dtype=out_dtype)
 
@@ -96,7 +124,7 @@ class Wkv(Mixer):
         gate = linear(mixed[3], self.w["g"])
         d = linear(linear(mixed[4], self.w["w1"], activation="tanh"), self.w["w2"], self.w0, out_dtype=torch.float32)
         o = ops.state_scan("wkv", r, k, v, step.state(cache_id, "matrix"), b.seq_start, b.seq_slot, b.n_seq,
-                           s.n_heads, s.head_dim, s.head_dim, decay_logits=d, bonus=self.u)
+                           s.n_heads, s.head_dim, s.head_dim, decay_logits=d, bonus=self.u, chunks=scan_chunks(b, h.device))
         y = ops.gated_group_norm(o, s.head_dim, self.norm, gate, "silu", s.eps, h.dtype)
         return linear(y, self.w["o"], None, residuals=residuals, out_dtype=out_dtype)
 

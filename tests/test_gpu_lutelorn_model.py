@@ -37,7 +37,7 @@ def test_whole_prompts(models, which, dtype):
     _, pcfg, w, model = models(which, dtype)
     engine = qs.Engine(model, max_tokens=512, max_batch=2)
     rng = np.random.default_rng(1)
-    for n in (1, 2, 63, 64, 65, 200):
+    for n in (1, 2, 63, 64, 65, 200, 389):       # from 256 tokens on the state mixers cut the prompt into chunks
         toks = random_tokens(rng, n, pcfg["vocab"])
         slot = engine.acquire()
         got = engine.step([slot], [toks], [all_places(n)]).cpu().numpy()
@@ -84,9 +84,10 @@ def test_batches_of_unequal_requests_and_reused_slots(models, which, dtype):
     """Prompts of unequal lengths in one step, then one token each until the shorter ones end; a second batch
     takes the slots and pages the first gave back (fewer pages than the two batches need together)."""
     _, pcfg, w, model = models(which, dtype)
-    engine = qs.Engine(model, max_tokens=64 * 7, max_batch=3)
+    engine = qs.Engine(model, max_tokens=64 * 8, max_batch=3)
     rng = np.random.default_rng(4)
-    for lens, prompt in (((130, 1, 67), (100, 1, 40)), ((64, 129, 3), (33, 128, 2)), ((90, 70, 110), (89, 1, 64))):
+    for lens, prompt in (((130, 1, 67), (100, 1, 40)), ((64, 129, 3), (33, 128, 2)), ((90, 70, 110), (89, 1, 64)),
+                         ((300, 20, 5), (290, 3, 1))):
         reqs = [random_tokens(rng, n, pcfg["vocab"]) for n in lens]
         refs = [P.logits_whole(pcfg, w, t) for t in reqs]
         slots = [engine.acquire() for _ in reqs]

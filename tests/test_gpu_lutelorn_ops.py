@@ -153,6 +153,62 @@ def test_wkv_state(H, d):
         close(got, ref, 2e-5, f"cuts {cuts[:4]}")
 
 
+@pytest.mark.parametrize("mode,H,dk,dv", [("decay", 3, 32, 48), ("decay", 2, 128, 64), ("wkv", 4, 64, 64), ("wkv", 1, 24, 24)])
+def test_chunks_side_by_side_equal_the_walk_in_order(mode, H, dk, dv):
+    """Three sequences of 300, 1 and 131 tokens cut into chunks of 64 (the last ones ragged), from states that
+    earlier steps left: outputs and final states equal those of the plain recurrence."""
+    rng = np.random.default_rng(dk)
+    lens = [300, 1, 131]
+    slots = [2, 0, 3]
+    T = sum(lens)
+    q, k, v = (rng.normal(0, 1, (T, H * d)) for d in (dk, dk, dv))
+    dlog, u, decay = rng.normal(-2.5, 1.0, (T, H * dk)), rng.normal(0, 0.5, (H, dk)), np.array([0.999, 0.9, 0.97, 0.5][:H])
+    kw = dict(head_decay=dev(decay)) if mode == "decay" else dict(decay_logits=dev(dlog), bonus=dev(u))
+    # a first step of 5 tokens per sequence leaves a state; the plain model sees both steps as one sequence
+    pre = [rng.normal(0, 1, (5, 3, H * max(dk, dv))) for _ in lens]
+    state = torch.zeros((4, H, dv, dk), device=DEV)
+    starts, chunk_starts, owners, row = [0], [0], [0], 0
+    for n in lens:
+        chunk_starts += [row + min(n, a + 64) for a in range(0, n, 64)]
+        row += n
+        starts.append(row)
+        owners.append(len(chunk_starts) - 1)
+    n_chunks = len(chunk_starts) - 1
+    for j, p in enumerate(pre):
+        kw0 = dict(kw)
+        if mode == "wkv":
+            kw0["decay_logits"] = dev(np.full((5, H * dk), -2.0))
+        ops.state_scan(mode, dev(p[:, 0, :H * dk]), dev(p[:, 1, :H * dk]), dev(p[:, 2, :H * dv]), state, i32([0, 5]), i32([slots[j]]), 1,
+                       H, dk, dv, **kw0)
+    got = ops.state_scan(mode, dev(q), dev(k), dev(v), state, i32(starts), i32(slots), 3, H, dk, dv,
+                         chunks=(i32(chunk_starts), i32(range(n_chunks)), i32(owners), n_chunks), **kw).cpu().numpy()
+    for j, (a, b) in enumerate(zip(starts, starts[1:])):
+        p = pre[j]
+        qq = np.concatenate([p[:, 0, :H * dk], q[a:b]]).reshape(-1, H, dk)
+        kk = np.concatenate([p[:, 1, :H * dk], k[a:b]]).reshape(-1, H, dk)
+        vv = np.concatenate([p[:, 2, :H * dv], v[a:b]]).reshape(-1, H, dv)
+        if mode == "decay":
+            ref = P.decayed_linear_attention(qq, kk, vv, decay)
+        else:
+            w = np.exp(-np.exp(np.concatenate([np.full((5, H * dk), -2.0), dlog[a:b]]))).reshape(-1, H, dk)
+            ref = P.wkv_recurrence(qq, kk, vv, w, u)
+        close(got[a:b], ref[5:].reshape(b - a, -1), 3e-5, f"sequence {j}")
+    # the states left behind: one more token per sequence must continue them
+    one = ops.state_scan(mode, dev(q[:3]), dev(k[:3]), dev(v[:3]), state, i32([0, 1, 2, 3]), i32(slots), 3, H, dk, dv,
+                         **(dict(kw, decay_logits=dev(dlog[:3])) if mode == "wkv" else kw)).cpu().numpy()
+    for j, (a, b) in enumerate(zip(starts, starts[1:])):
+        p = pre[j]
+        qq = np.concatenate([p[:, 0, :H * dk], q[a:b], q[j:j + 1]]).reshape(-1, H, dk)
+        kk = np.concatenate([p[:, 1, :H * dk], k[a:b], k[j:j + 1]]).reshape(-1, H, dk)
+        vv = np.concatenate([p[:, 2, :H * dv], v[a:b], v[j:j + 1]]).reshape(-1, H, dv)
+        if mode == "decay":
+            ref = P.decayed_linear_attention(qq, kk, vv, decay)
+        else:
+            w = np.exp(-np.exp(np.concatenate([np.full((5, H * dk), -2.0), dlog[a:b], dlog[j:j + 1]]))).reshape(-1, H, dk)
+            ref = P.wkv_recurrence(qq, kk, vv, w, u)
+        close(one[j], ref[-1].reshape(-1), 3e-5, f"the token after sequence {j}")
+
+
 def test_states_of_a_batch_with_idle_and_padding_sequences():
     """Three sequences of unequal lengths in one step, a sequence entry without a slot between them and rows that
     belong to nobody at the end: each sequence equals itself alone, the rest is zero."""
