@@ -16,7 +16,7 @@
 namespace {
 
 constexpr int RK = 32;              // key rows per thread
-constexpr int TILE = 8;             // tokens staged in shared memory at a time
+constexpr int TILE = 16;            // tokens staged in shared memory at a time
 
 // Which rows a thread owns: groups of four consecutive rows, dealt to the KS threads of a column in turn, so that
 // the threads' 16-byte accesses to a column of the state and to a token's q and k lie side by side.
@@ -30,7 +30,7 @@ __device__ __forceinline__ int row_of(int ks, int ks_log2, int r) { return 4 * (
 // PHASE 3: every chunk adds to its tokens' o what the state it started from contributes, decayed up to each token.
 // For phases 1 and 3 a "sequence" of the kernel is a chunk and its "slot" the chunk's place in the scratch.
 template <typename TI, bool WKV, int PHASE>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 state_scan_kernel(float* __restrict__ o, size_t ldo,
                   const TI* __restrict__ q, size_t ldq, const TI* __restrict__ k, size_t ldk,
                   const TI* __restrict__ v, size_t ldv, const float* __restrict__ dlog, size_t ldd,
@@ -97,23 +97,37 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
         // a thread stages one key row of the tile's tokens, in order: in PHASE 3 the row's decay since the chunk's
         // start runs along and q arrives multiplied by it
         for (int i = tid; i < dkp; i += blockDim.x) {
+            // all of the tile's loads first, so that they are in flight together
+            TI qraw[TILE], kraw[TILE];
+            float draw[TILE];
+#pragma unroll
+            for (int tt = 0; tt < TILE; ++tt) {
+                if (tt < nt && i < dk) {
+                    const size_t row = (size_t)(base + tt);
+                    qraw[tt] = q[row * ldq + h * dk + i];
+                    if (PHASE != 3) kraw[tt] = k[row * ldk + h * dk + i];
+                    if (WKV) draw[tt] = dlog[row * ldd + h * dk + i];
+                }
+            }
             float run = PHASE == 3 ? carry[i] : 1.0f;
-            for (int tt = 0; tt < nt; ++tt) {
-                const size_t row = (size_t)(base + tt);
-                float qv = 0.f, kv = 0.f, wv = 0.f;
-                if (i < dk) {
-                    qv = apply_activation(to_f32(q[row * ldq + h * dk + i]), in_act);
-                    if (PHASE != 3) kv = apply_activation(to_f32(k[row * ldk + h * dk + i]), in_act);
-                    if (WKV) wv = expf(-expf(dlog[row * ldd + h * dk + i]));
+#pragma unroll
+            for (int tt = 0; tt < TILE; ++tt) {
+                if (tt < nt) {
+                    float qv = 0.f, kv = 0.f, wv = 0.f;
+                    if (i < dk) {
+                        qv = apply_activation(to_f32(qraw[tt]), in_act);
+                        if (PHASE != 3) kv = apply_activation(to_f32(kraw[tt]), in_act);
+                        if (WKV) wv = expf(-expf(draw[tt]));
+                    }
+                    if (PHASE == 3) {
+                        if (WKV) { qv *= run; run *= wv; }
+                        else { run *= decay; qv *= run; }
+                    } else {
+                        sk[tt * dkp + i] = kv;
+                        if (WKV) sw[tt * dkp + i] = wv;
+                    }
+                    sq[tt * dkp + i] = qv;
                 }
-                if (PHASE == 3) {
-                    if (WKV) { qv *= run; run *= wv; }
-                    else { run *= decay; qv *= run; }
-                } else {
-                    sk[tt * dkp + i] = kv;
-                    if (WKV) sw[tt * dkp + i] = wv;
-                }
-                sq[tt * dkp + i] = qv;
             }
             if (PHASE == 3) carry[i] = run;
         }
@@ -157,8 +171,10 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
             }
             for (int off = KS >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
             if (owner && ks == 0) {
+                // PHASE 3 adds to what PHASE 1 wrote: this thread is the element's only writer in this kernel, and a
+                // reduction that returns nothing does not make the loop wait for the old value
                 float* dst = o + (size_t)(base + tt) * ldo + h * dv + col0 + col;
-                *dst = PHASE == 3 ? *dst + acc : acc;
+                if (PHASE == 3) atomicAdd(dst, acc); else *dst = acc;
             }
         }
     }
@@ -209,13 +225,25 @@ __global__ void chunk_prefix_kernel(float* __restrict__ chunk_state, const float
     const int c0 = seq_chunk[s], c1 = seq_chunk[s + 1];
     if (slot < 0 || c1 <= c0) return;
     const size_t n = (size_t)H * dv * dk;
+    constexpr int AHEAD = 8;                            // chunks whose loads are in flight together
     for (size_t e = (size_t)blockIdx.y * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.y * blockDim.x) {
         const int i = (int)(e % dk), h = (int)(e / ((size_t)dv * dk));
+        const float* dec = chunk_decay + (size_t)h * dk + i;
         float S = state[(size_t)slot * slot_stride + e];
-        for (int c = c0; c < c1; ++c) {
-            const float added = chunk_state[(size_t)c * n + e];
-            chunk_state[(size_t)c * n + e] = S;
-            S = fmaf(chunk_decay[(size_t)c * H * dk + (size_t)h * dk + i], S, added);
+        for (int c = c0; c < c1; c += AHEAD) {
+            float added[AHEAD], a[AHEAD];
+#pragma unroll
+            for (int g = 0; g < AHEAD; ++g) {
+                added[g] = c + g < c1 ? chunk_state[(size_t)(c + g) * n + e] : 0.f;
+                a[g] = c + g < c1 ? dec[(size_t)(c + g) * H * dk] : 1.f;
+            }
+#pragma unroll
+            for (int g = 0; g < AHEAD; ++g) {
+                if (c + g < c1) {
+                    chunk_state[(size_t)(c + g) * n + e] = S;
+                    S = fmaf(a[g], S, added[g]);
+                }
+            }
         }
         state[(size_t)slot * slot_stride + e] = S;
     }
@@ -263,9 +291,11 @@ int launch_scan(bool wkv, int phase, float* o, long long ldo, const void* q, lon
     const int vec = dk % 4 == 0 && slot_stride % 4 == 0 && ((uintptr_t)state % 16) == 0;
     dim3 grid(n_seq, H, (dv + cols - 1) / cols);
     cudaError_t e;
-#define GO(WKV, PHASE) e = qs_launch_dependent(state_scan_kernel<TI, WKV, PHASE>, grid, dim3(threads), smem, stream, o, (size_t)ldo, \
+#define GO(WKV, PHASE) do { e = smem > 48 * 1024 ? cudaFuncSetAttribute(state_scan_kernel<TI, WKV, PHASE>, \
+            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) : cudaSuccess; \
+    if (e == cudaSuccess) e = qs_launch_dependent(state_scan_kernel<TI, WKV, PHASE>, grid, dim3(threads), smem, stream, o, (size_t)ldo, \
         (const TI*)q, (size_t)ldq, (const TI*)k, (size_t)ldk, (const TI*)v, (size_t)ldv, dlog, (size_t)ldd, head_decay, bonus, \
-        bonus_dtype, state, (size_t)slot_stride, seq_start, seq_slot, n_seq, T_rows, H, dk, dv, ks_log2, cols, in_act, vec)
+        bonus_dtype, state, (size_t)slot_stride, seq_start, seq_slot, n_seq, T_rows, H, dk, dv, ks_log2, cols, in_act, vec); } while (0)
     if (wkv) { if (phase == 0) GO(true, 0); else if (phase == 1) GO(true, 1); else GO(true, 3); }
     else { if (phase == 0) GO(false, 0); else if (phase == 1) GO(false, 1); else GO(false, 3); }
 #undef GO

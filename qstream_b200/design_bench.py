@@ -155,24 +155,30 @@ def kernel_table(torch, np, pk, width=2048, T=4096, batch=32, ctx=2048):
         ab = torch.randn(n_rows, 2 * width * 8 // 3, device=dev, dtype=bf)
         add(f"gated activation {tag}", "(in GPT-J's product)", t.kernel(lambda: ops.gated_act(ab, "silu")), ab.numel() * 3)
 
-    # matrix states: one prompt of T tokens, and `batch` single tokens
+    # matrix states: one prompt of T tokens (cut into chunks, as the mixers do from 256 tokens on), and `batch` single tokens
+    from .parts.recurrent import CHUNK_TOKENS
+    n_chunks = T // CHUNK_TOKENS
+    chunks = (i32(list(range(0, T + 1, CHUNK_TOKENS))), i32(list(range(n_chunks))), i32([0, n_chunks]), n_chunks)
+    one_start, one_slot = i32([0, T]), i32([0])
+    dec_start, dec_slot = i32(list(range(batch + 1))), i32(list(range(batch)))
     for mode, heads, dk in (("decay", H, d), ("wkv", width // 64, 64)):
         n = heads * dk
         q, k, v = (torch.randn(T, n, device=dev, dtype=bf) for _ in range(3))
         state = torch.zeros(batch, heads, dk, dk, device=dev)
         extra = dict(head_decay=torch.full((heads,), 0.99, device=dev)) if mode == "decay" else \
             dict(decay_logits=torch.randn(T, n, device=dev), bonus=torch.randn(heads, dk, device=dev, dtype=bf))
-        ms = t.kernel(lambda: ops.state_scan(mode, q, k, v, state, i32([0, T]), i32([0]), 1, heads, dk, dk, **extra), repeats=3)
-        add(f"state scan {mode} prompt {T}", "attention prompt", ms, flops=4.0 * T * heads * dk * dk, bound="fp32")
+        ms = t.kernel(lambda: ops.state_scan(mode, q, k, v, state, one_start, one_slot, 1, heads, dk, dk, chunks=chunks, **extra))
+        # the chunks' own part and the part of the state they start from: 2 + 1 multiply-adds per state element and token
+        add(f"state scan {mode} prompt {T} (4 kernels)", "attention prompt", ms, flops=6.0 * T * heads * dk * dk, bound="fp32")
         qd, kd, vd = q[:batch], k[:batch], v[:batch]
         if mode == "wkv":
             extra["decay_logits"] = extra["decay_logits"][:batch]
-        ms = t.kernel(lambda: ops.state_scan(mode, qd, kd, vd, state, i32(list(range(batch + 1))), i32(list(range(batch))), batch,
-                                             heads, dk, dk, **extra))
+        ms = t.kernel(lambda: ops.state_scan(mode, qd, kd, vd, state, dec_start, dec_slot, batch, heads, dk, dk, **extra))
         add(f"state scan {mode} decode {batch}", "attention decode", ms, 2 * state.numel() * 4)
 
     # attention: prompt of T tokens, decode of `batch` tokens at context ctx; GPT-J's form (values as wide as keys, no
     # cap, no gate, a key head per query head) and Lutelorn's (grouped keys, capped scores, gate)
+    dslot, dpos = i32(list(range(batch))), i32([ctx - 1] * batch)
     for name, g_heads, cap, gated in (("(GPT-J)", H, 0.0, False), ("capped, gated, grouped", G, 30.0, True)):
         n_pages = batch * ctx // 64
         kc = torch.randn(n_pages, g_heads, 64, d, device=dev, dtype=bf)
@@ -183,13 +189,14 @@ def kernel_table(torch, np, pk, width=2048, T=4096, batch=32, ctx=2048):
         gate = torch.randn(T, H * d, device=dev, dtype=bf) if gated else None
         tl = min(T, ctx)
         tiles = torch.tensor([(a, min(128, tl - a), a, 0) for a in range(0, tl, 128)][::-1], dtype=torch.int32, device=dev)
-        ms = t.kernel(lambda: attention_bf16.prefill(q[:tl], H, g_heads, d, d ** -0.5, 0, tiles, table, 64, kc, vc, status,
-                                                     softcap=cap, gate=gate[:tl] if gated else None))
+        qp, gp = q[:tl], (gate[:tl] if gated else None)
+        ms = t.kernel(lambda: attention_bf16.prefill(qp, H, g_heads, d, d ** -0.5, 0, tiles, table, 64, kc, vc, status,
+                                                     softcap=cap, gate=gp))
         add(f"attention prompt {tl} {name}", "" if not gated else "attention prompt (GPT-J)", ms, flops=4.0 * H * d * tl * tl / 2, bound="tensor")
         qd = q[:batch].contiguous()
         gd = gate[:batch].contiguous() if gated else None
-        ms = t.kernel(lambda: attention_bf16.decode(qd, H, g_heads, d, d ** -0.5, 0, i32(list(range(batch))), i32([ctx - 1] * batch),
-                                                    table, 64, kc, vc, ctx, status, softcap=cap, gate=gd))
+        ms = t.kernel(lambda: attention_bf16.decode(qd, H, g_heads, d, d ** -0.5, 0, dslot, dpos, table, 64, kc, vc, ctx, status,
+                                                    softcap=cap, gate=gd))
         add(f"attention decode {batch} x {ctx} {name}", "" if not gated else "attention decode (GPT-J)", ms, batch * ctx * g_heads * d * 4)
     return rows
 

@@ -139,7 +139,7 @@ def test_decay_attention_state(H, dk, dv):
         close(got, ref, 2e-5, f"cuts {cuts[:4]}")
 
 
-@pytest.mark.parametrize("H,d", [(6, 64), (1, 24), (3, 16), (2, 128)])
+@pytest.mark.parametrize("H,d", [(6, 64), (1, 24), (3, 16), (2, 128), (1, 256)])
 def test_wkv_state(H, d):
     rng = np.random.default_rng(d)
     T = 100
