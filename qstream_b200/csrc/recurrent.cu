@@ -8,14 +8,15 @@
 // The state lives in 32-bit, per slot as [heads][dv][dk] (a column of S is contiguous), starts at zero and is
 // read at the start of a step and written back at its end; everything between the projections and the output is
 // 32-bit arithmetic.  One kernel serves prompts and single tokens: a block owns some columns of one head of one
-// sequence and walks the sequence's tokens of this step in order.  A thread owns RK consecutive key rows of one
-// column; the KS threads of a column are neighbours in a warp and add their parts of o by shuffles, in a fixed
-// order, so a token's result does not depend on the batch or on how the prompt was cut.
+// sequence and walks the sequence's tokens of this step in order.  A thread owns RK key rows of two neighbouring
+// columns; the KS threads of a pair of columns are neighbours in a warp and add their parts of o by shuffles, in a
+// fixed order, so a token's result does not depend on the batch or on how the prompt was cut.
 #include "common.cuh"
 
 namespace {
 
-constexpr int RK = 32;              // key rows per thread
+constexpr int RK = 16;              // key rows per thread and column
+constexpr int CPT = 2;              // columns per thread: a token's q and k are read from shared memory once for both
 constexpr int TILE = 16;            // tokens staged in shared memory at a time
 
 // Which rows a thread owns: groups of four consecutive rows, dealt to the KS threads of a column in turn, so that
@@ -64,25 +65,27 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
         return;
     }
     if (t1 <= t0) return;
-    const int col = tid >> ks_log2, ks = tid & (KS - 1);
-    const bool owner = col < n_cols;
-    float* scol = state + (size_t)slot * slot_stride + ((size_t)h * dv + col0 + (owner ? col : 0)) * dk;
+    const int pair = tid >> ks_log2, ks = tid & (KS - 1);
+    const bool own0 = CPT * pair < n_cols, own1 = CPT * pair + 1 < n_cols;
+    float* scol0 = state + (size_t)slot * slot_stride + ((size_t)h * dv + col0 + (own0 ? CPT * pair : 0)) * dk;
+    float* scol1 = state + (size_t)slot * slot_stride + ((size_t)h * dv + col0 + (own1 ? CPT * pair + 1 : 0)) * dk;
 
-    float S[RK], u[RK];
+    float S0[RK], S1[RK], u[RK];
 #pragma unroll
     for (int r4 = 0; r4 < RK / 4; ++r4) {
         const int i = row_of(ks, ks_log2, 4 * r4);
-        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (PHASE != 1 && owner) {
-            if (vec) { if (i < dk) x = *reinterpret_cast<const float4*>(scol + i); }
-            else {
-                if (i < dk) x.x = scol[i];
-                if (i + 1 < dk) x.y = scol[i + 1];
-                if (i + 2 < dk) x.z = scol[i + 2];
-                if (i + 3 < dk) x.w = scol[i + 3];
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f), y = x;
+        if (PHASE != 1) {
+            if (vec) {
+                if (own0 && i < dk) x = *reinterpret_cast<const float4*>(scol0 + i);
+                if (own1 && i < dk) y = *reinterpret_cast<const float4*>(scol1 + i);
+            } else {
+                if (own0) { if (i < dk) x.x = scol0[i]; if (i + 1 < dk) x.y = scol0[i + 1]; if (i + 2 < dk) x.z = scol0[i + 2]; if (i + 3 < dk) x.w = scol0[i + 3]; }
+                if (own1) { if (i < dk) y.x = scol1[i]; if (i + 1 < dk) y.y = scol1[i + 1]; if (i + 2 < dk) y.z = scol1[i + 2]; if (i + 3 < dk) y.w = scol1[i + 3]; }
             }
         }
-        S[4 * r4] = x.x; S[4 * r4 + 1] = x.y; S[4 * r4 + 2] = x.z; S[4 * r4 + 3] = x.w;
+        S0[4 * r4] = x.x; S0[4 * r4 + 1] = x.y; S0[4 * r4 + 2] = x.z; S0[4 * r4 + 3] = x.w;
+        S1[4 * r4] = y.x; S1[4 * r4 + 1] = y.y; S1[4 * r4 + 2] = y.z; S1[4 * r4 + 3] = y.w;
 #pragma unroll
         for (int j = 0; j < 4; ++j)
             u[4 * r4 + j] = (WKV && PHASE != 3 && i + j < dk) ? load_as_f32(bonus, bonus_dtype, (size_t)h * dk + i + j) : 0.f;
@@ -138,55 +141,71 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
             }
         __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {
-            const float vj = PHASE == 3 ? 0.f : sv[tt * cols + (owner ? col : 0)];
+            const float v0 = (PHASE == 3 || !own0) ? 0.f : sv[tt * cols + CPT * pair];
+            const float v1 = (PHASE == 3 || !own1) ? 0.f : sv[tt * cols + CPT * pair + 1];
             const float4* q4 = reinterpret_cast<const float4*>(sq + tt * dkp) + ks;
             const float4* k4 = reinterpret_cast<const float4*>(sk + tt * dkp) + ks;
             const float4* w4 = reinterpret_cast<const float4*>(sw + tt * dkp) + ks;
-            float acc = 0.f;
+            float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
             for (int r4 = 0; r4 < RK / 4; ++r4) {
                 const float4 qq = q4[r4 << ks_log2];
                 const float qa[4] = {qq.x, qq.y, qq.z, qq.w};
                 if (PHASE == 3) {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) acc = fmaf(qa[j], S[r4 * 4 + j], acc);
-                    continue;
-                }
-                const float4 kk = k4[r4 << ks_log2];
-                const float ka[4] = {kk.x, kk.y, kk.z, kk.w};
-                float wa[4] = {0.f, 0.f, 0.f, 0.f};
-                if (WKV) { const float4 ww = w4[r4 << ks_log2]; wa[0] = ww.x; wa[1] = ww.y; wa[2] = ww.z; wa[3] = ww.w; }
+                    for (int j = 0; j < 4; ++j) {
+                        acc0 = fmaf(qa[j], S0[r4 * 4 + j], acc0);
+                        acc1 = fmaf(qa[j], S1[r4 * 4 + j], acc1);
+                    }
+                } else {
+                    const float4 kk = k4[r4 << ks_log2];
+                    const float ka[4] = {kk.x, kk.y, kk.z, kk.w};
+                    float wa[4] = {0.f, 0.f, 0.f, 0.f};
+                    if (WKV) { const float4 ww = w4[r4 << ks_log2]; wa[0] = ww.x; wa[1] = ww.y; wa[2] = ww.z; wa[3] = ww.w; }
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int r = r4 * 4 + j;
-                    const float kv = ka[j] * vj;
-                    if (WKV) {
-                        acc = fmaf(qa[j], fmaf(u[r], kv, S[r]), acc);
-                        S[r] = fmaf(wa[j], S[r], kv);
-                    } else {
-                        S[r] = fmaf(decay, S[r], kv);
-                        acc = fmaf(qa[j], S[r], acc);
+                    for (int j = 0; j < 4; ++j) {
+                        const int r = r4 * 4 + j;
+                        const float kv0 = ka[j] * v0, kv1 = ka[j] * v1;
+                        if (WKV) {
+                            acc0 = fmaf(qa[j], fmaf(u[r], kv0, S0[r]), acc0);
+                            acc1 = fmaf(qa[j], fmaf(u[r], kv1, S1[r]), acc1);
+                            S0[r] = fmaf(wa[j], S0[r], kv0);
+                            S1[r] = fmaf(wa[j], S1[r], kv1);
+                        } else {
+                            S0[r] = fmaf(decay, S0[r], kv0);
+                            S1[r] = fmaf(decay, S1[r], kv1);
+                            acc0 = fmaf(qa[j], S0[r], acc0);
+                            acc1 = fmaf(qa[j], S1[r], acc1);
+                        }
                     }
                 }
             }
-            for (int off = KS >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-            if (owner && ks == 0) {
+            for (int off = KS >> 1; off > 0; off >>= 1) {
+                acc0 += __shfl_xor_sync(0xffffffffu, acc0, off);
+                acc1 += __shfl_xor_sync(0xffffffffu, acc1, off);
+            }
+            if (ks == 0) {
                 // PHASE 3 adds to what PHASE 1 wrote: this thread is the element's only writer in this kernel, and a
                 // reduction that returns nothing does not make the loop wait for the old value
-                float* dst = o + (size_t)(base + tt) * ldo + h * dv + col0 + col;
-                if (PHASE == 3) atomicAdd(dst, acc); else *dst = acc;
+                float* dst = o + (size_t)(base + tt) * ldo + h * dv + col0 + CPT * pair;
+                if (own0) { if (PHASE == 3) atomicAdd(dst, acc0); else dst[0] = acc0; }
+                if (own1) { if (PHASE == 3) atomicAdd(dst + 1, acc1); else dst[1] = acc1; }
             }
         }
     }
-    if (PHASE != 3 && owner) {
+    if (PHASE != 3) {
 #pragma unroll
         for (int r4 = 0; r4 < RK / 4; ++r4) {
             const int i = row_of(ks, ks_log2, 4 * r4);
-            if (vec) { if (i < dk) *reinterpret_cast<float4*>(scol + i) = make_float4(S[4 * r4], S[4 * r4 + 1], S[4 * r4 + 2], S[4 * r4 + 3]); }
-            else {
+            if (vec) {
+                if (own0 && i < dk) *reinterpret_cast<float4*>(scol0 + i) = make_float4(S0[4 * r4], S0[4 * r4 + 1], S0[4 * r4 + 2], S0[4 * r4 + 3]);
+                if (own1 && i < dk) *reinterpret_cast<float4*>(scol1 + i) = make_float4(S1[4 * r4], S1[4 * r4 + 1], S1[4 * r4 + 2], S1[4 * r4 + 3]);
+            } else {
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    if (i + j < dk) scol[i + j] = S[4 * r4 + j];
+                for (int j = 0; j < 4; ++j) {
+                    if (own0 && i + j < dk) scol0[i + j] = S0[4 * r4 + j];
+                    if (own1 && i + j < dk) scol1[i + j] = S1[4 * r4 + j];
+                }
             }
         }
     }
@@ -281,11 +300,11 @@ int launch_scan(bool wkv, int phase, float* o, long long ldo, const void* q, lon
     int ks_log2 = 0;
     while ((RK << ks_log2) < dk) ++ks_log2;
     const int KS = 1 << ks_log2;
-    int cols = 256 / KS;
-    if (cols > dv) cols = dv;
+    int cols = CPT * 256 / KS;
+    if (cols > dv) cols = (dv + CPT - 1) / CPT * CPT;
     // few sequences and heads: narrower blocks, so that more SMs take part
-    while (cols > 8 && (long long)n_seq * H * ((dv + cols - 1) / cols) < 148 && cols * KS > 64) cols >>= 1;
-    const int threads = ((cols * KS + 31) / 32) * 32;
+    while (cols > 8 * CPT && (long long)n_seq * H * ((dv + cols - 1) / cols) < 148 && cols / CPT * KS > 64) cols >>= 1;
+    const int threads = ((cols / CPT * KS + 31) / 32) * 32;
     const int dkp = KS * RK;
     const size_t smem = ((size_t)TILE * ((wkv ? 3 : 2) * dkp + cols) + dkp) * sizeof(float);
     const int vec = dk % 4 == 0 && slot_stride % 4 == 0 && ((uintptr_t)state % 16) == 0;
@@ -322,7 +341,7 @@ QS_API int qs_state_scan(int mode, float* o, long long ldo, const void* q, long 
                          float* chunk_state, float* chunk_decay, cudaStream_t stream) {
     if (n_seq == 0 || T_rows == 0) return QS_OK;
     QS_REQUIRE(n_seq > 0 && T_rows > 0 && H > 0 && dk > 0 && dv > 0, "state_scan: bad sizes");
-    QS_REQUIRE(dk <= 8 * RK, "state_scan: %d key channels per head above %d", dk, 8 * RK);
+    QS_REQUIRE(dk <= 16 * RK, "state_scan: %d key channels per head above %d", dk, 16 * RK);
     QS_REQUIRE(H <= 65535, "state_scan: %d heads exceed the grid", H);
     QS_REQUIRE(mode == 0 ? head_decay != nullptr : (mode == 1 && dlog && bonus), "state_scan: mode %d lacks its operands", mode);
     QS_REQUIRE(dtype == QS_F32 || dtype == QS_BF16, "state_scan: unknown dtype %d", dtype);
