@@ -41,7 +41,9 @@ def main(argv=None) -> int:
         ops.library()
         model = load_model(args.model, dtype=args.dtype, device="cuda")
         page = 64
-        max_tokens = max(page, -(-args.max_tokens // page) * page)
+        # --max-tokens counts the requests' tokens; the cache hands out whole pages, so every live request may hold
+        # up to a page less one of padding on top: room for 64 requests' worth of it
+        max_tokens = max(page, -(-args.max_tokens // page) * page) + 64 * page
         max_batch = args.max_batch or max(1, max_tokens // page)
         engine = Engine(model, max_tokens=max_tokens, max_batch=max_batch)
     except QStreamError as e:

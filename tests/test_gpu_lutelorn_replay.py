@@ -44,7 +44,7 @@ def test_replay_and_command_line(tmp_path, which, dtype):
             {"id": k + "b", "tokens": [reqs[k][prompt[k] + j]], "want": [0] if j % 2 else []} for k in ("q0", "q2")]})
         if j % 2:
             where[len(steps) - 1] = [(k, prompt[k] + j) for k in ("q0", "q2")]
-    text = "".join(json.dumps(s) + "\\n" for s in steps)
+    text = "".join(json.dumps(s) + "\n" for s in steps)
     out = tmp_path / "out"
     proc = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype,
                            "--out", str(out), "--max-tokens", "512"], input=text, text=True, capture_output=True, timeout=600)
