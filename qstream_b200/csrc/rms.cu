@@ -112,14 +112,28 @@ int launch_gated(void* out, long long ldo, const void* o, long long ldi, const v
 
 // ----------------------------------------------------------------------------- gated activation
 
-template <typename T>
-__global__ void gated_act_kernel(T* __restrict__ out, size_t ldo, const T* __restrict__ ab, size_t ldi, int F, int act,
-                                 size_t total) {
+// One row per blockIdx.x, a block of columns per blockIdx.y.  VEC (bfloat16, F a multiple of 8, 16-byte aligned
+// rows): eight columns per thread as one 16-byte piece of each half.
+template <typename T, bool VEC>
+__global__ void gated_act_kernel(T* __restrict__ out, size_t ldo, const T* __restrict__ ab, size_t ldi, int F, int act) {
     grid_dep_launch();
     grid_dep_wait();
-    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
-        const size_t r = e / F;
-        const int c = (int)(e - r * F);
+    const size_t r = blockIdx.x;
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * (VEC ? 8 : 1);
+    if (c >= F) return;
+    if (VEC) {
+        const uint4 a = *reinterpret_cast<const uint4*>(ab + r * ldi + c), b = *reinterpret_cast<const uint4*>(ab + r * ldi + F + c);
+        const uint32_t au[4] = {a.x, a.y, a.z, a.w}, bu[4] = {b.x, b.y, b.z, b.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float a0 = __uint_as_float(au[j] << 16), a1 = __uint_as_float(au[j] & 0xffff0000u);
+            const float b0 = __uint_as_float(bu[j] << 16), b1 = __uint_as_float(bu[j] & 0xffff0000u);
+            const __nv_bfloat162 p = __floats2bfloat162_rn(apply_activation(a0, act) * b0, apply_activation(a1, act) * b1);
+            o[j] = *reinterpret_cast<const uint32_t*>(&p);
+        }
+        *reinterpret_cast<uint4*>(out + r * ldo + c) = make_uint4(o[0], o[1], o[2], o[3]);
+    } else {
         const float a = to_f32(ab[r * ldi + c]), b = to_f32(ab[r * ldi + F + c]);
         out[r * ldo + c] = from_f32<T>(apply_activation(a, act) * b);
     }
@@ -224,16 +238,25 @@ QS_API int qs_gated_act(void* out, long long ldo, const void* ab, long long ldi,
                         cudaStream_t stream) {
     if (rows == 0) return QS_OK;
     QS_REQUIRE(rows > 0 && F > 0 && ldi >= 2 * (long long)F && ldo >= F, "gated_act: bad sizes rows=%d F=%d", rows, F);
-    const size_t total = (size_t)rows * F;
-    const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+    typedef __nv_bfloat16 bf16;
     cudaError_t e;
-    if (dtype == QS_F32)
-        e = qs_launch_dependent(gated_act_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)out, (size_t)ldo,
-                                (const float*)ab, (size_t)ldi, F, act, total);
-    else if (dtype == QS_BF16)
-        e = qs_launch_dependent(gated_act_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)out,
-                                (size_t)ldo, (const __nv_bfloat16*)ab, (size_t)ldi, F, act, total);
-    else return qs_fail(QS_ERR_INVALID_INPUT, "gated_act: unknown dtype %d", dtype);
+    if (dtype == QS_BF16 && F % 8 == 0 && ldi % 8 == 0 && ldo % 8 == 0 && ((uintptr_t)ab % 16) == 0 && ((uintptr_t)out % 16) == 0) {
+        const int threads = F >= 2048 ? 256 : 64;
+        const int by = (F / 8 + threads - 1) / threads;
+        QS_REQUIRE(by <= 65535, "gated_act: %d columns exceed the grid", F);
+        e = qs_launch_dependent(gated_act_kernel<bf16, true>, dim3(rows, by), dim3(threads), 0, stream, (bf16*)out, (size_t)ldo,
+                                (const bf16*)ab, (size_t)ldi, F, act);
+    } else {
+        const int by = (F + 255) / 256;
+        QS_REQUIRE(by <= 65535, "gated_act: %d columns exceed the grid", F);
+        if (dtype == QS_F32)
+            e = qs_launch_dependent(gated_act_kernel<float, false>, dim3(rows, by), dim3(256), 0, stream, (float*)out, (size_t)ldo,
+                                    (const float*)ab, (size_t)ldi, F, act);
+        else if (dtype == QS_BF16)
+            e = qs_launch_dependent(gated_act_kernel<bf16, false>, dim3(rows, by), dim3(256), 0, stream, (bf16*)out, (size_t)ldo,
+                                    (const bf16*)ab, (size_t)ldi, F, act);
+        else return qs_fail(QS_ERR_INVALID_INPUT, "gated_act: unknown dtype %d", dtype);
+    }
     if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "gated_act: %s", cudaGetErrorString(e));
     return qs_check_launch("gated_act");
 }

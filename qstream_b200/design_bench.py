@@ -152,7 +152,7 @@ def kernel_table(torch, np, pk, width=2048, T=4096, batch=32, ctx=2048):
         slot = i32([0] * n_rows) if tag == "prompt" else i32(list(range(batch)))
         pos = i32(list(range(n_rows))) if tag == "prompt" else i32([ctx - 1] * batch)
         add(f"token shift {tag}", "layernorm", t.kernel(lambda: ops.token_shift(xb, mu, last, slot, pos)), n_rows * width * 12)
-        ab = torch.randn(n_rows, 2 * width * 8 // 3, device=dev, dtype=bf)
+        ab = torch.randn(n_rows, 2 * ((width * 8 // 3 + 255) // 256 * 256), device=dev, dtype=bf)     # the models' feed-forward width
         add(f"gated activation {tag}", "(in GPT-J's product)", t.kernel(lambda: ops.gated_act(ab, "silu")), ab.numel() * 3)
 
     # matrix states: one prompt of T tokens (cut into chunks, as the mixers do from 256 tokens on), and `batch` single tokens

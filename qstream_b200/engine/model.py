@@ -170,10 +170,16 @@ class CausalLM:
         x = self.embedding.forward(step)
         if record is not None:
             ops.check_finite(x, n_runs, record, b.tok_slot)
+        settle = getattr(step, "settle", lambda t: t)
         for i, run in enumerate(self.spec.schedule):
-            x = self.blocks[run.layer].forward(x, step, run.cache)
+            block = self.blocks[run.layer]
+            if not getattr(block, "takes_pending", False):
+                x = settle(x)                               # a layer that wants the stream with nothing left to add
+            x = block.forward(x, step, run.cache)
             if record is not None:
+                x = settle(x)
                 ops.check_finite(x, i, record, b.tok_slot)
+        x = settle(x)
         if b.n_want == 0:
             return None
         rows = ops.gather_rows(x, b.want_rows)

@@ -93,6 +93,16 @@ class StepContext:
         self.nan_record = nan_record
         # what one layer leaves for later layers of the same step (tensors of the step's tokens)
         self.scratch = {}
+        # a layer's last branch that is not yet added to the residual stream (an object with `apply(x)`): the next
+        # layer may take it over (arrangements with `takes_pending`), anyone else calls `settle` first
+        self.pending = None
+
+    def settle(self, x):
+        """The residual stream with nothing pending."""
+        if self.pending is not None:
+            pending, self.pending = self.pending, None
+            x = pending.apply(x)
+        return x
 
     def kv(self, cache_id: int):
         return self.cache.view(cache_id)

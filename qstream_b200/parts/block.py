@@ -148,12 +148,28 @@ class SequentialBlock(Arrangement):
         return self.ffn.forward(self.norms["post_mixer"].forward(x), step, residuals=(x,))
 
 
+class PendingUpdate:
+    """A branch that is still to be added to the 32-bit stream: x += mult * branch.  The layer that ends with it
+    leaves it to the next layer's first norm, which adds it in the same kernel; whoever needs the stream itself
+    (`StepContext.settle`) adds it with a kernel of its own."""
+
+    def __init__(self, branch, mult):
+        self.branch, self.mult = branch, mult
+
+    def apply(self, x):
+        from ..csrc import ops
+        ops.rmsnorm(x, None, 0.0, update=self.branch, mult=self.mult, want_norm=False)
+        return x
+
+
 class ScaledResidualBlock(Arrangement):
     """x += m mixer(norm_1(x)); x += m ffn(norm_2(x)), with the residual stream x in 32-bit whatever the engine's
     type (the embedding delivers it so) and updated in place; a layer may have no feed-forward.  The branches'
     results arrive in 32-bit from their last product; the update x + m y and the norm that follows it are one
-    kernel.  Norms must offer `forward_update` (the RMS norm does)."""
+    kernel, also across layers: a layer leaves its last branch pending (`step.pending`) for the next layer's first
+    norm.  Norms must offer `forward_update` (the RMS norm does)."""
     norm_names = ("input",)
+    takes_pending = True
 
     def __init__(self, spec, parts, runtime):
         super().__init__(spec, parts, runtime)
@@ -184,14 +200,14 @@ class ScaledResidualBlock(Arrangement):
         return {"out_dtype": self.wide} if self._typed[id(part)] else {}
 
     def forward(self, x, step, cache_id):
-        from ..csrc import ops
-        y = self.mixer.forward(self.norms["input"].forward(x), step, cache_id, **self._wide(self.mixer))
-        if self.ffn is None:
-            ops.rmsnorm(x, None, 0.0, update=y, mult=self.mult, want_norm=False)
-            return x
-        h = self.norms["post_mixer"].forward_update(x, y, self.mult)
-        z = self.ffn.forward(h, step, **self._wide(self.ffn))
-        ops.rmsnorm(x, None, 0.0, update=z, mult=self.mult, want_norm=False)
+        before, step.pending = step.pending, None
+        norm = self.norms["input"]
+        h = norm.forward_update(x, before.branch, before.mult) if before is not None else norm.forward(x)
+        y = self.mixer.forward(h, step, cache_id, **self._wide(self.mixer))
+        if self.ffn is not None:
+            h = self.norms["post_mixer"].forward_update(x, y, self.mult)
+            y = self.ffn.forward(h, step, **self._wide(self.ffn))
+        step.pending = PendingUpdate(y, self.mult)
         return x
 
 

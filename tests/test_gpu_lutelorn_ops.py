@@ -58,10 +58,14 @@ def test_gated_group_norm(n, group):
     close(got, ref, 3e-6, "no weight, no gate")
 
 
-def test_gated_activation():
-    rng = np.random.default_rng(0)
-    ab = rng.normal(0, 2, (9, 2 * 50))
-    close(ops.gated_act(dev(ab), "silu"), P.silu(ab[:, :50]) * ab[:, 50:], 2e-6)
+@pytest.mark.parametrize("F", [50, 64, 2056])
+def test_gated_activation(F):
+    rng = np.random.default_rng(F)
+    ab = rng.normal(0, 2, (9, 2 * F))
+    close(ops.gated_act(dev(ab), "silu"), P.silu(ab[:, :F]) * ab[:, F:], 2e-6)
+    abb = dev(ab, torch.bfloat16)
+    ref = abb.float().cpu().numpy().astype(np.float64)
+    close(ops.gated_act(abb, "silu"), P.silu(ref[:, :F]) * ref[:, F:], 5e-3, "bfloat16")
 
 
 def test_pair_embedding_across_steps():
