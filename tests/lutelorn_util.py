@@ -69,7 +69,20 @@ CONFIG_C = {
         attention_layer(2, 1, 16, 80, rot=None, softcap=20.0, scale=0.2, mlp=None),
     ],
 }
-CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C}
+# D: heads whose sizes do not add up to the width, one key head for five query heads, a value size that only the
+#    generic attention kernel takes beside one that the tensor-core kernel takes, every layer with a feed-forward.
+CONFIG_D = {
+    "architecture": "Lutelorn", "vocab": 1000, "width": 160, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+    "embedding": {"scale": 2.0, "bigram": {"buckets": 997, "mul_prev": 1000003, "mul_cur": 999983}},
+    "layers": [
+        wkv_layer(5, 32, mlp=DENSE(200)),
+        attention_layer(5, 1, 48, 32, rot=(24, 1e6), softcap=30.0, v_mix=True, mlp=DENSE(136)),
+        lightning_layer(48, 16, [0.6, 0.99, 0.9999], mlp=DENSE(264)),
+        attention_layer(5, 1, 48, 32, rot=(24, 1e6), softcap=30.0, v_mix=True, mlp=DENSE(136)),
+        attention_layer(2, 2, 24, 40, rot=(8, 100.0), softcap=2.0, scale=0.5, mlp=DENSE(64)),
+    ],
+}
+CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "D": CONFIG_D}
 
 
 def make_weights(cfg: dict, seed: int, decay_rank: int = 5) -> dict[str, np.ndarray]:
@@ -130,7 +143,7 @@ def write_folder(folder, cfg: dict, weights: dict, dtype: str):
 
 def make_folder(tmp_path, which: str, dtype: str, seed: int = 0):
     cfg = CONFIGS[which]
-    return write_folder(tmp_path / f"lutelorn_{which}_{dtype}", cfg, make_weights(cfg, seed + "ABC".index(which)), dtype), cfg
+    return write_folder(tmp_path / f"lutelorn_{which}_{dtype}", cfg, make_weights(cfg, seed + "ABCD".index(which)), dtype), cfg
 
 
 def logits_error(got, ref):

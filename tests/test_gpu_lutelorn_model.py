@@ -11,7 +11,8 @@ from util import random_tokens
 
 pytestmark = pytest.mark.gpu
 
-CASES = [("A", "float32"), ("B", "float32"), ("A", "bfloat16"), ("B", "bfloat16"), ("C", "float32"), ("C", "bfloat16")]
+CASES = [("A", "float32"), ("B", "float32"), ("A", "bfloat16"), ("B", "bfloat16"), ("C", "float32"), ("C", "bfloat16"),
+         ("D", "float32"), ("D", "bfloat16")]
 
 
 @pytest.fixture(scope="module")
