@@ -202,6 +202,200 @@ decode_split_kernel(float* __restrict__ partial, const __nv_bfloat16* __restrict
     }
 }
 
+// The same for HG query heads that share a key head: one pass over the page's keys and values serves them all
+// (a CTA per query head reads the pages once per head, all but once from L2).  blockIdx.y = the group of HG
+// query heads; the partial results are laid out per query head as above, so the merge kernel is the same.
+// The sums of each head are taken in the same order as in the one-head kernel.
+template <int NCH, int UNROLL, int HG>
+__global__ void __launch_bounds__(WARPS * 32)
+decode_split_group_kernel(float* __restrict__ partial, const __nv_bfloat16* __restrict__ q, size_t ldq,
+                          const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
+                          const int32_t* __restrict__ page_table, int max_pages,
+                          const int32_t* __restrict__ tok_slot, const int32_t* __restrict__ tok_pos,
+                          int n_heads, int n_kv_heads, int dh, int gs_log2, float scale, int window, int max_splits,
+                          int32_t* __restrict__ status, int dv, float softcap) {
+    __shared__ float s_scores[WARPS][HG][PAGE];
+    __shared__ float s_m[WARPS][HG], s_l[WARPS][HG];
+    extern __shared__ float s_acc[];                 // [WARPS][HG][dv]
+
+    const int split = blockIdx.x, head0 = blockIdx.y * HG, t = blockIdx.z;
+    const int slot = tok_slot[t];
+    if (slot < 0) return;
+    const int pos = tok_pos[t];
+    if (pos < 0 || pos >= max_splits * SPLIT) {
+        if (threadIdx.x == 0 && split == 0 && blockIdx.y == 0) atomicExch(status, 1);
+        return;
+    }
+    const int first = window > 0 ? max(0, pos - window + 1) : 0;
+    if (split * SPLIT > pos || (split + 1) * SPLIT <= first) return;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int GS = 1 << gs_log2, KPL = 32 >> gs_log2;
+    const int chunk = lane & (GS - 1), sub = lane >> gs_log2;
+    const int n_chunks = dh >> 3, v_chunks = dv >> 3;
+    const int kvh = head0 / (n_heads / n_kv_heads);
+
+    float qf[HG][NCH][8];
+#pragma unroll
+    for (int g = 0; g < HG; ++g) {
+        const __nv_bfloat16* qrow = q + (size_t)t * ldq + (size_t)(head0 + g) * dh;
+#pragma unroll
+        for (int i = 0; i < NCH; ++i) {
+            const int c = chunk + i * GS;
+            if (c < n_chunks) bf16x8_to_f32(*reinterpret_cast<const uint4*>(qrow + c * 8), qf[g][i]);
+            else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) qf[g][i][j] = 0.f;
+            }
+        }
+    }
+    float acc[HG][NCH][8];
+#pragma unroll
+    for (int g = 0; g < HG; ++g)
+#pragma unroll
+        for (int i = 0; i < NCH; ++i)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[g][i][j] = 0.f;
+    float m[HG], l[HG];
+#pragma unroll
+    for (int g = 0; g < HG; ++g) { m[g] = -INFINITY; l[g] = 0.f; }
+
+    const int key0 = split * SPLIT + warp * PAGE;
+    if (key0 <= pos && key0 + PAGE > first) {
+        const int page = page_table[(size_t)slot * max_pages + (key0 >> 6)];
+        if (page < 0) {
+            if (lane == 0) atomicExch(status, 3);
+        } else {
+            const size_t base = ((size_t)page * n_kv_heads + kvh) * PAGE;
+            const __nv_bfloat16* kp = k_cache + base * dh;
+            const __nv_bfloat16* vp = v_cache + base * dv;
+            const int n_keys = min(PAGE, pos - key0 + 1);
+            for (int it0 = 0; it0 * KPL < n_keys; it0 += UNROLL) {
+                uint4 raw[UNROLL][NCH];
+#pragma unroll
+                for (int u = 0; u < UNROLL; ++u) {
+                    const int kk = (it0 + u) * KPL + sub;
+#pragma unroll
+                    for (int i = 0; i < NCH; ++i) {
+                        const int c = chunk + i * GS;
+                        raw[u][i] = (kk < n_keys && c < n_chunks)
+                            ? __ldg(reinterpret_cast<const uint4*>(kp + (size_t)kk * dh + c * 8)) : make_uint4(0, 0, 0, 0);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < UNROLL; ++u) {
+                    const int kk = (it0 + u) * KPL + sub;
+                    float kf[NCH][8];
+#pragma unroll
+                    for (int i = 0; i < NCH; ++i) bf16x8_to_f32(raw[u][i], kf[i]);
+#pragma unroll
+                    for (int g = 0; g < HG; ++g) {
+                        float dot = 0.f;
+#pragma unroll
+                        for (int i = 0; i < NCH; ++i)
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) dot = fmaf(qf[g][i][j], kf[i][j], dot);
+                        for (int o = GS >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                        float sc = dot * scale;
+                        if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);
+                        if (chunk == 0 && kk < PAGE) s_scores[warp][g][kk] = (kk < n_keys && key0 + kk >= first) ? sc : -INFINITY;
+                    }
+                }
+            }
+            __syncwarp();
+#pragma unroll
+            for (int g = 0; g < HG; ++g) {
+                const float s0 = lane < n_keys ? s_scores[warp][g][lane] : -INFINITY;
+                const float s1 = lane + 32 < n_keys ? s_scores[warp][g][lane + 32] : -INFINITY;
+                m[g] = warp_max(fmaxf(s0, s1));
+                const float p0 = m[g] == -INFINITY ? 0.f : expf(s0 - m[g]);
+                const float p1 = m[g] == -INFINITY ? 0.f : expf(s1 - m[g]);
+                l[g] = warp_sum(p0 + p1);
+                __syncwarp();
+                s_scores[warp][g][lane] = p0;
+                s_scores[warp][g][lane + 32] = p1;
+            }
+            __syncwarp();
+            for (int it0 = 0; it0 * KPL < n_keys; it0 += UNROLL) {
+                uint4 raw[UNROLL][NCH];
+#pragma unroll
+                for (int u = 0; u < UNROLL; ++u) {
+                    const int kk = (it0 + u) * KPL + sub;
+#pragma unroll
+                    for (int i = 0; i < NCH; ++i) {
+                        const int c = chunk + i * GS;
+                        raw[u][i] = (kk < n_keys && c < v_chunks)
+                            ? __ldg(reinterpret_cast<const uint4*>(vp + (size_t)kk * dv + c * 8)) : make_uint4(0, 0, 0, 0);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < UNROLL; ++u) {
+                    const int kk = (it0 + u) * KPL + sub;
+#pragma unroll
+                    for (int i = 0; i < NCH; ++i) {
+                        float vf[8];
+                        bf16x8_to_f32(raw[u][i], vf);
+#pragma unroll
+                        for (int g = 0; g < HG; ++g) {
+                            const float pw = kk < n_keys ? s_scores[warp][g][kk] : 0.f;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) acc[g][i][j] = fmaf(pw, vf[j], acc[g][i][j]);
+                        }
+                    }
+                }
+            }
+            for (int o = GS; o < 32; o <<= 1) {
+#pragma unroll
+                for (int g = 0; g < HG; ++g)
+#pragma unroll
+                    for (int i = 0; i < NCH; ++i)
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) acc[g][i][j] += __shfl_xor_sync(0xffffffffu, acc[g][i][j], o);
+            }
+        }
+    }
+
+    if (lane == 0) {
+#pragma unroll
+        for (int g = 0; g < HG; ++g) { s_m[warp][g] = m[g]; s_l[warp][g] = l[g]; }
+    }
+    if (sub == 0) {
+#pragma unroll
+        for (int g = 0; g < HG; ++g)
+#pragma unroll
+            for (int i = 0; i < NCH; ++i) {
+                const int c = chunk + i * GS;
+                if (c < v_chunks) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) s_acc[((size_t)warp * HG + g) * dv + c * 8 + j] = acc[g][i][j];
+                }
+            }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < HG; ++g) {
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) M = fmaxf(M, s_m[w][g]);
+        float* out = partial + (((size_t)t * n_heads + head0 + g) * max_splits + split) * (dv + 2);
+        for (int d = threadIdx.x; d < dv; d += blockDim.x) {
+            float o = 0.f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w)
+                if (s_m[w][g] != -INFINITY) o += s_acc[((size_t)w * HG + g) * dv + d] * expf(s_m[w][g] - M);
+            out[d] = o;
+        }
+        if (threadIdx.x == 0) {
+            float L = 0.f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w)
+                if (s_m[w][g] != -INFINITY) L += s_l[w][g] * expf(s_m[w][g] - M);
+            out[dv] = M;
+            out[dv + 1] = L;
+        }
+    }
+}
+
 // One block per (token, head): add the splits' partial results in ascending split order.
 // `dh` is the values' head size here.  `gate` (may be null): the row is multiplied by sigmoid(gate) on its way out.
 __global__ void decode_merge_kernel(__nv_bfloat16* __restrict__ out, size_t ldo, const float* __restrict__ partial,
@@ -330,11 +524,24 @@ QS_API int qs_attention_decode_ex(void* out, long long ldo, const void* q, long 
         scratch, (const __nv_bfloat16*)q, (size_t)ldq, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
         page_table, max_pages, tok_slot, tok_pos, n_heads, n_kv_heads, dh, gs_log2, scale, window, max_splits, status, \
         dv, softcap)
-    if (nch == 1) GO(1, 8);
+    // Query heads that share a key head go through the pages together, two to a CTA (chunk slots of one or two per
+    // lane only).  Four to a CTA were measured slower (32 x 2,048 keys, 16 query and 4 key heads of 128: 108 us
+    // against 81 us with two and 96 us with one): four heads' accumulators leave room for three CTAs per SM and
+    // two loads in flight per lane.
+    const int per_group = n_heads / n_kv_heads;
+    const int hg = (nch <= 2 && per_group % 2 == 0) ? 2 : 1;
+#define GROUP(NCH, UNROLL, HG) decode_split_group_kernel<NCH, UNROLL, HG><<<dim3(max_splits, n_heads / HG, T_tokens), WARPS * 32, \
+        smem * HG, stream>>>(scratch, (const __nv_bfloat16*)q, (size_t)ldq, (const __nv_bfloat16*)k_cache, \
+        (const __nv_bfloat16*)v_cache, page_table, max_pages, tok_slot, tok_pos, n_heads, n_kv_heads, dh, gs_log2, scale, window, \
+        max_splits, status, dv, softcap)
+    if (hg == 2 && nch == 1) GROUP(1, 8, 2);
+    else if (hg == 2) GROUP(2, 4, 2);
+    else if (nch == 1) GO(1, 8);
     else if (nch == 3) GO(3, 4);
     else if (nch == 5) GO(5, 2);
     else if (few_ctas) GO(2, 8);
     else GO(2, 4);
+#undef GROUP
 #undef GO
     int rc = qs_check_launch("attention_decode");
     if (rc != QS_OK) return rc;

@@ -300,7 +300,9 @@ def test_attention_with_a_far_key_that_wins(H, G, dk, dv, softcap, rot, dtype):
 
 @pytest.mark.parametrize("H,G,dk,dv,softcap,rot", [(4, 2, 64, 32, 8.0, (32, 1e4)), (2, 1, 32, 64, 0.0, (16, 1e5)),
                                                      (2, 2, 80, 80, 20.0, None), (3, 1, 128, 16, 5.0, (64, 1e6)),
-                                                     (2, 2, 16, 256, 0.0, None), (1, 1, 256, 48, 50.0, (256, 1e4))])
+                                                     (2, 2, 16, 256, 0.0, None), (1, 1, 256, 48, 50.0, (256, 1e4)),
+                                                     (8, 2, 128, 128, 30.0, (64, 1e6)), (8, 1, 64, 32, 0.0, (64, 1e4)),
+                                                     (12, 2, 32, 48, 6.0, None), (4, 1, 192, 64, 0.0, None)])
 def test_tensor_core_and_split_attention_kernels(H, G, dk, dv, softcap, rot):
     rng = np.random.default_rng(dk + 7 * dv)
     T = 330
