@@ -11,12 +11,14 @@ norm          forward(x) -> y
 position      apply(q, k, step, n_heads, n_kv_heads, head_dim): change q [T, H*dh] and k
               in place, from step.batch.tok_pos; a rotary kind may instead offer
               `fused_table` and `rotary_dim`, which attention fuses with its cache write
-mixer         kv_need() -> KvNeed | None; state_need() -> StateNeed | None;
-              forward(h, step, cache_id, residuals=()) -> [T, width]
+mixer         kv_need() -> KvNeed | None; state_need() -> StateNeed | {name: StateNeed} | None;
+              forward(h, step, cache_id, residuals=()) -> [T, width] (an optional `out_dtype`
+              argument lets an arrangement with a 32-bit stream ask for the result in 32-bit)
 feed_forward  forward(h, step, residuals=()) -> [T, width]
 arrangement   forward(x, step, cache_id) -> x'; built from the block's parts
-embedding     forward(step) -> x [T, width] in the activations' type, from step.batch.tokens (and, for
-              position tables, step.batch.tok_pos)
+embedding     forward(step) -> x [T, width] in the activations' type (or wider: a 32-bit stream), from
+              step.batch.tokens (and, for position tables, step.batch.tok_pos); optional state_need()
+              for state per sequence, found under step.state("embedding")
 head          forward(rows) -> float32 logits [n, vocab] of the wanted rows (already normalised by the
               model's final norm, if it has one); `tie(embedding)` if its spec says `tied`
 

@@ -25,6 +25,8 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to 64)")
     ap.add_argument("--max-batch", type=int, default=0, help="most live requests (default: what the cache allows)")
+    ap.add_argument("--padding-pages", type=int, default=64,
+                    help="cache pages on top of --max-tokens for the requests' padding to whole pages (default: 64)")
     args = ap.parse_args(argv)
 
     print("[qstream] trace_run: loading the library (the kernels are compiled at the first call) ...",
@@ -42,8 +44,8 @@ def main(argv=None) -> int:
         model = load_model(args.model, dtype=args.dtype, device="cuda")
         page = 64
         # --max-tokens counts the requests' tokens; the cache hands out whole pages, so every live request may hold
-        # up to a page less one of padding on top: room for 64 requests' worth of it
-        max_tokens = max(page, -(-args.max_tokens // page) * page) + 64 * page
+        # up to a page less one of padding on top: room for --padding-pages requests' worth of it
+        max_tokens = max(page, -(-args.max_tokens // page) * page) + max(0, args.padding_pages) * page
         max_batch = args.max_batch or max(1, max_tokens // page)
         engine = Engine(model, max_tokens=max_tokens, max_batch=max_batch)
     except QStreamError as e:

@@ -94,7 +94,7 @@ def test_replay_reports_a_cache_that_is_too_small(tmp_path):
     steps = [{"step": 0, "entries": [{"id": "a", "tokens": list(range(70)), "want": [69]}], "end": []}]
     text = json.dumps(steps[0]) + "\n"
     proc = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", "float32",
-                           "--out", str(tmp_path / "o"), "--max-tokens", "64"], input=text, text=True,
+                           "--out", str(tmp_path / "o"), "--max-tokens", "64", "--padding-pages", "0"], input=text, text=True,
                           capture_output=True, timeout=600)
     assert proc.returncode == 1 and "cache pages" in proc.stderr and "done" not in proc.stdout
 
