@@ -140,6 +140,17 @@ __global__ void rope_store_vec_kernel(__nv_bfloat16* __restrict__ q, const __nv_
     if (n_kv_heads == 0) return;
     if (page < 0) { if (threadIdx.x == 0) atomicExch(status, 2); return; }
     const size_t in_page = (size_t)(pos & (page_tokens - 1));
+    if (dv == dh && !v_first) {             // values as wide as keys and kept as they are: one item moves a chunk of each
+        for (int e = tid; e < n_kv_heads * hc; e += stride) {
+            const int kvh = e / hc, c = e - kvh * hc;
+            const size_t dst = (((size_t)page * n_kv_heads + kvh) * page_tokens + in_page) * dh + c * 8;
+            uint4 kk = *reinterpret_cast<const uint4*>(k + (size_t)t * ldk + (size_t)kvh * dh + c * 8);
+            if (rotate && c < rc) kk = rotate8(kk, cs + c * 8);
+            *reinterpret_cast<uint4*>(k_cache + dst) = kk;
+            *reinterpret_cast<uint4*>(v_cache + dst) = *reinterpret_cast<const uint4*>(v + (size_t)t * ldv + (size_t)kvh * dh + c * 8);
+        }
+        return;
+    }
     const int vc = dv >> 3;                                              // 16-byte chunks of a head's values
     for (int e = tid; e < n_kv_heads * (hc + vc); e += stride) {
         const int kvh = e / (hc + vc), c = e - kvh * (hc + vc);

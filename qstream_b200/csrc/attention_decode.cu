@@ -30,15 +30,17 @@ __device__ __forceinline__ void bf16x8_to_f32(const uint4& raw, float (&f)[8]) {
 // Lanes are grouped GS to a key (GS = the power of two >= dh / 16, at most 32); lane `c` of a group
 // owns the 16-byte chunks c, c + GS, ... (NCH of them) of the head.  KPL = 32 / GS keys are
 // handled per warp instruction.
-template <int NCH, int UNROLL>
+// EXT = false is the plain form (values as wide as keys, no cap); its code must stay within 72 registers.
+template <int NCH, int UNROLL, bool EXT>
 __global__ void __launch_bounds__(WARPS * 32)
 decode_split_kernel(float* __restrict__ partial, const __nv_bfloat16* __restrict__ q, size_t ldq,
                     const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
                     const int32_t* __restrict__ page_table, int max_pages,
                     const int32_t* __restrict__ tok_slot, const int32_t* __restrict__ tok_pos,
                     int n_heads, int n_kv_heads, int dh, int gs_log2, float scale, int window, int max_splits,
-                    int32_t* __restrict__ status, int dv, float softcap) {
-    // dv: the values' head size (the keys' is dh); softcap c > 0: scores become c tanh(s / c)
+                    int32_t* __restrict__ status, int dv_arg, float softcap) {
+    // EXT: dv_arg is the values' head size (the keys' is dh); softcap c > 0: scores become c tanh(s / c)
+    const int dv = EXT ? dv_arg : dh;
     __shared__ float s_scores[WARPS][PAGE];
     __shared__ float s_m[WARPS], s_l[WARPS];
     extern __shared__ float s_acc[];                 // [WARPS][dv]
@@ -57,7 +59,7 @@ decode_split_kernel(float* __restrict__ partial, const __nv_bfloat16* __restrict
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int GS = 1 << gs_log2, KPL = 32 >> gs_log2;
     const int chunk = lane & (GS - 1), sub = lane >> gs_log2;
-    const int n_chunks = dh >> 3, v_chunks = dv >> 3;
+    const int n_chunks = dh >> 3, v_chunks = EXT ? dv >> 3 : n_chunks;
     const int kvh = head / (n_heads / n_kv_heads);
 
     // this lane's part of the query, in 32-bit
@@ -116,7 +118,7 @@ decode_split_kernel(float* __restrict__ partial, const __nv_bfloat16* __restrict
                     }
                     for (int o = GS >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
                     float sc = dot * scale;
-                    if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);
+                    if (EXT && softcap > 0.f) sc = softcap * tanhf(sc / softcap);
                     if (chunk == 0 && kk < PAGE) s_scores[warp][kk] = (kk < n_keys && key0 + kk >= first) ? sc : -INFINITY;
                 }
             }
@@ -520,7 +522,9 @@ QS_API int qs_attention_decode_ex(void* out, long long ldo, const void* q, long 
         sm_counts[dev] = sm_count;
     }
     const bool few_ctas = (long long)max_splits * n_heads * T_tokens <= 2LL * sm_count;
-#define GO(NCH, UNROLL) decode_split_kernel<NCH, UNROLL><<<grid, WARPS * 32, smem, stream>>>( \
+    const bool ext = dv != dh || softcap > 0.f;
+#define GO(NCH, UNROLL) do { if (ext) GO1(NCH, UNROLL, true); else GO1(NCH, UNROLL, false); } while (0)
+#define GO1(NCH, UNROLL, EXT) decode_split_kernel<NCH, UNROLL, EXT><<<grid, WARPS * 32, smem, stream>>>( \
         scratch, (const __nv_bfloat16*)q, (size_t)ldq, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
         page_table, max_pages, tok_slot, tok_pos, n_heads, n_kv_heads, dh, gs_log2, scale, window, max_splits, status, \
         dv, softcap)
@@ -543,6 +547,7 @@ QS_API int qs_attention_decode_ex(void* out, long long ldo, const void* q, long 
     else GO(2, 4);
 #undef GROUP
 #undef GO
+#undef GO1
     int rc = qs_check_launch("attention_decode");
     if (rc != QS_OK) return rc;
     decode_merge_kernel<<<dim3(n_heads, T_tokens), dv >= 128 ? 128 : 64, (size_t)3 * max_splits * sizeof(float), stream>>>(

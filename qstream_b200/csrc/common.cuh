@@ -151,11 +151,11 @@ __device__ __forceinline__ float apply_activation(float v, int act) {
     return v;
 }
 
+// The tensor-core products' epilogues take the two GELU forms only: more cases in this chain slowed every
+// epilogue of the matrix products, also those without an activation (a 256 x 16384 x 4096 product with gelu_new twice
+// as long).  Other activations after such a product are a kernel of their own (`qs_activate`).
 __device__ __forceinline__ float apply_activation_fast(float v, int act) {
     if (act == QS_ACT_GELU_TANH) return gelu_tanh_fast(v);
     if (act == QS_ACT_GELU_ERF) return gelu_erf(v);
-    if (act == QS_ACT_SILU) return __fdividef(v, 1.0f + __expf(-v));
-    if (act == QS_ACT_SIGMOID) return __fdividef(1.0f, 1.0f + __expf(-v));
-    if (act == QS_ACT_TANH) return 1.0f - __fdividef(2.0f, __expf(2.0f * v) + 1.0f);
     return v;
 }

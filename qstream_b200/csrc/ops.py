@@ -41,6 +41,7 @@ _SIGNATURES = {
                              c_longlong, c_float, c_void_p, c_int, c_float, c_int, c_int, c_float, c_void_p], c_int),
     "qs_gated_group_norm": ([c_void_p, c_int, c_longlong, c_void_p, c_int, c_longlong, c_void_p, c_int, c_void_p, c_int,
                              c_longlong, c_int, c_int, c_int, c_int, c_float, c_void_p], c_int),
+    "qs_activate": ([c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p], c_int),
     "qs_gated_act": ([c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p], c_int),
     "qs_embedding_hashed": ([c_void_p, c_int, c_void_p, c_void_p, c_int, c_float, c_longlong, c_longlong, c_longlong,
                              c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p], c_int),
@@ -318,6 +319,13 @@ def gated_group_norm(o, group: int, weight, gate, gate_activation, eps: float, o
                                         _code(weight), ptr(gate), _code(gate), ldg, ACTIVATIONS[gate_activation],
                                         rows, n, int(group), float(eps), stream()))
     return out
+
+
+def activate(x: torch.Tensor, activation) -> torch.Tensor:
+    """x <- act(x) in place (32-bit arithmetic, rounded once)."""
+    rows, n, ld = _rows(x)
+    check(library().qs_activate(ptr(x), ld, dtype_code(x), rows, n, ACTIVATIONS[activation], stream()))
+    return x
 
 
 def gated_act(ab: torch.Tensor, activation) -> torch.Tensor:

@@ -5,6 +5,7 @@
 //   gated_group_norm   out = o / sqrt(mean_group(o^2) + eps) * w * act(gate), groups of consecutive elements
 //                      (one group = the whole row, or one per head; group 0 = no norm, only the gate)
 //   gated_act          out = act(a) * b for the two halves [a | b] of a fused projection (gated feed-forward)
+//   activate           x <- act(x) in place
 //   embedding_hashed   x = table[token] * scale + pair_table[hash(previous token, token)]
 //   keep_last_rows     state[slot] = the last row each sequence brought in this step
 //
@@ -139,6 +140,15 @@ __global__ void gated_act_kernel(T* __restrict__ out, size_t ldo, const T* __res
     }
 }
 
+// x <- act(x), in 32-bit, rounded once: for activations that the matrix products' epilogues do not offer.
+template <typename T>
+__global__ void activate_kernel(T* __restrict__ x, size_t ld, int n, int act) {
+    grid_dep_launch();
+    grid_dep_wait();
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c < n) x[(size_t)blockIdx.x * ld + c] = from_f32<T>(apply_activation(to_f32(x[(size_t)blockIdx.x * ld + c]), act));
+}
+
 // ----------------------------------------------------------------------------- hashed-pair embedding
 
 // x[t] = table[token] * scale + pair[row], row = (previous * mul_prev + token * mul_cur) mod buckets, and row
@@ -259,6 +269,20 @@ QS_API int qs_gated_act(void* out, long long ldo, const void* ab, long long ldi,
     }
     if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "gated_act: %s", cudaGetErrorString(e));
     return qs_check_launch("gated_act");
+}
+
+QS_API int qs_activate(void* x, long long ld, int dtype, int rows, int n, int act, cudaStream_t stream) {
+    if (rows == 0 || n == 0) return QS_OK;
+    QS_REQUIRE(rows > 0 && n > 0 && ld >= n && (n + 255) / 256 <= 65535, "activate: bad sizes rows=%d n=%d", rows, n);
+    cudaError_t e;
+    if (dtype == QS_F32)
+        e = qs_launch_dependent(activate_kernel<float>, dim3(rows, (n + 255) / 256), dim3(256), 0, stream, (float*)x, (size_t)ld, n, act);
+    else if (dtype == QS_BF16)
+        e = qs_launch_dependent(activate_kernel<__nv_bfloat16>, dim3(rows, (n + 255) / 256), dim3(256), 0, stream,
+                                (__nv_bfloat16*)x, (size_t)ld, n, act);
+    else return qs_fail(QS_ERR_INVALID_INPUT, "activate: unknown dtype %d", dtype);
+    if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "activate: %s", cudaGetErrorString(e));
+    return qs_check_launch("activate");
 }
 
 QS_API int qs_embedding_hashed(void* out, int out_dtype, const void* table, const void* pair, int table_dtype, float scale,

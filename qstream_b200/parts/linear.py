@@ -11,6 +11,8 @@ import torch
 
 from ..csrc import ops
 
+TENSOR_CORE_ACTIVATIONS = (None, "none", "gelu_new", "gelu")
+
 
 def linear(x, weight, bias=None, activation=None, residuals=(), out_dtype=None, out=None) -> torch.Tensor:
     """`out`: an optional view [M, N] with contiguous rows (any row stride) to write into."""
@@ -18,7 +20,10 @@ def linear(x, weight, bias=None, activation=None, residuals=(), out_dtype=None, 
     if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
         from ..csrc import gemm_tc
         if gemm_tc.takes(x, weight):
-            return gemm_tc.linear(x, weight, bias, activation, residuals, out_dtype, out)
+            if activation in TENSOR_CORE_ACTIVATIONS:
+                return gemm_tc.linear(x, weight, bias, activation, residuals, out_dtype, out)
+            if not residuals:       # an activation that the tensor-core epilogue does not offer: a kernel of its own behind it
+                return ops.activate(gemm_tc.linear(x, weight, bias, None, (), out_dtype, out), activation)
     return ops.linear_simt(x, weight, bias, activation, residuals, out_dtype, out)
 
 
