@@ -26,12 +26,12 @@ def lutelorn_config(width: int, layers: int) -> dict:
     kinds = {
         "lightning": {"type": "lightning", "mixer": {"heads": heads, "dim": 128, "vdim": 128, "decay": decay}, "mlp": mlp},
         "attention": {"type": "attention", "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128,
-                                                     "rot": {"dims": 64, "base": 1e6}, "scale": 128 ** -0.5, "softcap": 30.0,
+                                                     "rot": {"dims": 64, "base": 10000.0}, "scale": 128 ** -0.5, "softcap": 50.0,
                                                      "v_mix": True}, "mlp": mlp},
         "wkv": {"type": "wkv", "mixer": {"heads": width // 64, "dim": 64, "decay_rank": 64}, "mlp": mlp},
     }
     order = ["lightning", "attention", "lightning", "wkv"]
-    return {"architecture": "Lutelorn", "vocab": VOCAB, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.7,
+    return {"architecture": "Lutelorn", "vocab": VOCAB, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.8,
             "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31337, "mul_cur": 7919}},
             "layers": [kinds[order[i % 4]] for i in range(layers)], "max_positions": 8192}
 
@@ -179,7 +179,7 @@ def kernel_table(torch, np, pk, width=2048, T=4096, batch=32, ctx=2048):
     # attention: prompt of T tokens, decode of `batch` tokens at context ctx; GPT-J's form (values as wide as keys, no
     # cap, no gate, a key head per query head) and Lutelorn's (grouped keys, capped scores, gate)
     dslot, dpos = i32(list(range(batch))), i32([ctx - 1] * batch)
-    for name, g_heads, cap, gated in (("(GPT-J)", H, 0.0, False), ("capped, gated, grouped", G, 30.0, True)):
+    for name, g_heads, cap, gated in (("(GPT-J)", H, 0.0, False), ("capped, gated, grouped", G, 50.0, True)):
         n_pages = batch * ctx // 64
         kc = torch.randn(n_pages, g_heads, 64, d, device=dev, dtype=bf)
         vc = torch.randn(n_pages, g_heads, 64, d, device=dev, dtype=bf)

@@ -48,13 +48,13 @@ CONFIG_A = {
 #    head rotated, values as wide as keys, no cap, no blending, a residual factor and an embedding scale of 1,
 #    no pair table, one head, sizes that are no multiples of 8 or 16.
 CONFIG_B = {
-    "architecture": "Lutelorn", "vocab": 131, "width": 48, "norm": {"eps": 1e-6}, "residual_mult": 1.0,
+    "architecture": "Lutelorn", "vocab": 131, "width": 48, "norm": {"eps": 2e-6}, "residual_mult": 1.0,
     "embedding": {"scale": 1.0},
     "layers": [
         wkv_layer(1, 24, mlp=DENSE(50)),
         attention_layer(3, 3, 12, 12, rot=(12, 500.0), mlp=None),
         lightning_layer(20, 12, [0.93], mlp=DENSE(64)),
-        attention_layer(6, 1, 10, 14, rot=(4, 1e6), softcap=12.0, mlp=DENSE(40)),
+        attention_layer(6, 1, 10, 14, rot=(4, 2e5), softcap=12.0, mlp=DENSE(40)),
     ],
 }
 # C: head sizes that the bfloat16 tensor-core attention takes (multiples of 16), values narrower and wider than keys.
@@ -72,13 +72,13 @@ CONFIG_C = {
 # D: heads whose sizes do not add up to the width, one key head for five query heads, a value size that only the
 #    generic attention kernel takes beside one that the tensor-core kernel takes, every layer with a feed-forward.
 CONFIG_D = {
-    "architecture": "Lutelorn", "vocab": 1000, "width": 160, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+    "architecture": "Lutelorn", "vocab": 1000, "width": 160, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
     "embedding": {"scale": 2.0, "bigram": {"buckets": 997, "mul_prev": 1000003, "mul_cur": 999983}},
     "layers": [
         wkv_layer(5, 32, mlp=DENSE(200)),
-        attention_layer(5, 1, 48, 32, rot=(24, 1e6), softcap=30.0, v_mix=True, mlp=DENSE(136)),
+        attention_layer(5, 1, 48, 32, rot=(24, 3e5), softcap=25.0, v_mix=True, mlp=DENSE(136)),
         lightning_layer(48, 16, [0.6, 0.99, 0.9999], mlp=DENSE(264)),
-        attention_layer(5, 1, 48, 32, rot=(24, 1e6), softcap=30.0, v_mix=True, mlp=DENSE(136)),
+        attention_layer(5, 1, 48, 32, rot=(24, 3e5), softcap=25.0, v_mix=True, mlp=DENSE(136)),
         attention_layer(2, 2, 24, 40, rot=(8, 100.0), softcap=2.0, scale=0.5, mlp=DENSE(64)),
     ],
 }

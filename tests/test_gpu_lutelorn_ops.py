@@ -36,9 +36,9 @@ def test_rms_norm_and_update(D, offset):
     h = ops.rmsnorm(dev(x), dev(w), 1e-5, offset)
     close(h, P.rms_norm(x, w, 1e-5, offset), 2e-6, "norm")
     xd = dev(x)
-    h = ops.rmsnorm(xd, dev(w), 1e-5, offset, out_dtype=torch.bfloat16, update=dev(y), mult=0.7)
-    close(xd, x + 0.7 * y, 1e-6, "update in place")
-    close(h, P.rms_norm(x + 0.7 * y, w, 1e-5, offset), 6e-3, "norm after the update, bfloat16")
+    h = ops.rmsnorm(xd, dev(w), 1e-5, offset, out_dtype=torch.bfloat16, update=dev(y), mult=0.6)
+    close(xd, x + 0.6 * y, 1e-6, "update in place")
+    close(h, P.rms_norm(x + 0.6 * y, w, 1e-5, offset), 6e-3, "norm after the update, bfloat16")
     xd = dev(x)
     assert ops.rmsnorm(xd, None, 0.0, update=dev(y, torch.bfloat16), mult=-2.0, want_norm=False) is None
     close(xd, x - 2.0 * dev(y, torch.bfloat16).float().cpu().numpy(), 1e-6, "update alone, bfloat16 branch")
@@ -127,7 +127,7 @@ def scan_in_steps(mode, q, k, v, cuts, H, dk, dv, dtype=torch.float32, **kw):
     return np.concatenate(out)
 
 
-@pytest.mark.parametrize("H,dk,dv", [(4, 32, 32), (3, 24, 40), (2, 64, 16), (1, 96, 128), (2, 128, 128), (1, 200, 8)])
+@pytest.mark.parametrize("H,dk,dv", [(4, 32, 16), (3, 24, 40), (2, 64, 16), (1, 96, 128), (2, 128, 128), (1, 200, 8)])
 def test_decay_attention_state(H, dk, dv):
     rng = np.random.default_rng(dk + dv)
     T = 150
@@ -143,7 +143,7 @@ def test_decay_attention_state(H, dk, dv):
         close(got, ref, 2e-5, f"cuts {cuts[:4]}")
 
 
-@pytest.mark.parametrize("H,d", [(6, 64), (1, 24), (3, 16), (2, 128), (1, 256)])
+@pytest.mark.parametrize("H,d", [(5, 64), (1, 24), (3, 16), (2, 128), (1, 256)])
 def test_wkv_state(H, d):
     rng = np.random.default_rng(d)
     T = 100
@@ -271,7 +271,7 @@ def paged_attention(q, k, v, H, G, dk, dv, scale, softcap, dtype, page_order, ro
     return out
 
 
-@pytest.mark.parametrize("H,G,dk,dv,softcap,rot", [(4, 2, 96, 64, 30.0, (48, 1e6)), (3, 3, 12, 12, 0.0, (12, 500.0)),
+@pytest.mark.parametrize("H,G,dk,dv,softcap,rot", [(4, 2, 80, 48, 25.0, (40, 3e5)), (3, 3, 12, 12, 0.0, (12, 500.0)),
                                                      (6, 1, 10, 14, 4.0, None), (2, 2, 64, 64, 0.0, (16, 1e4)),
                                                      (8, 4, 32, 128, 8.0, (32, 1e4))])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -299,9 +299,9 @@ def test_attention_with_a_far_key_that_wins(H, G, dk, dv, softcap, rot, dtype):
 
 
 @pytest.mark.parametrize("H,G,dk,dv,softcap,rot", [(4, 2, 64, 32, 8.0, (32, 1e4)), (2, 1, 32, 64, 0.0, (16, 1e5)),
-                                                     (2, 2, 80, 80, 20.0, None), (3, 1, 128, 16, 5.0, (64, 1e6)),
+                                                     (2, 2, 80, 80, 20.0, None), (3, 1, 128, 16, 5.0, (64, 2e6)),
                                                      (2, 2, 16, 256, 0.0, None), (1, 1, 256, 48, 50.0, (256, 1e4)),
-                                                     (8, 2, 128, 128, 30.0, (64, 1e6)), (8, 1, 64, 32, 0.0, (64, 1e4)),
+                                                     (8, 2, 128, 128, 20.0, (64, 5e5)), (8, 1, 64, 32, 0.0, (64, 1e4)),
                                                      (12, 2, 32, 48, 6.0, None), (4, 1, 192, 64, 0.0, None)])
 def test_tensor_core_and_split_attention_kernels(H, G, dk, dv, softcap, rot):
     rng = np.random.default_rng(dk + 7 * dv)
