@@ -38,6 +38,33 @@ class RmsNormSpec:
 
 
 @dataclass(frozen=True)
+class StreamNormSpec:
+    """A norm with a weight and no bias that reads a residual stream in its own type (32-bit, say) and writes the
+    engine's: the layer norm (x - mean) / sqrt(variance + eps) * w (`center`) or the RMS norm x / sqrt(mean(x^2) + eps)
+    * w, eps inside the root.  It can also add a branch to the stream first, the branch normed with another such
+    norm's weight, in the same kernel (layers that norm a branch before they add it)."""
+    size: int
+    eps: float
+    center: bool = True
+    kind: str = "stream_norm"
+    names: Mapping[str, str] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class RotaryHalfSpec:
+    """Rotary position encoding on the first `rotary_dim` dims of a vector, element i paired with i + rotary_dim/2,
+    angle position * f_i, f_i = base^(-2i / rotary_dim).  `scaling` (factor, original, fast, slow) rescales the
+    frequencies in the YaRN manner: with dim(t) = rotary_dim ln(original / (2 pi t)) / (2 ln base),
+    lo = max(floor(dim(fast)), 0), hi = min(ceil(dim(slow)), rotary_dim - 1) and
+    ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), f_i becomes f_i / factor * ramp_i + f_i (1 - ramp_i), and cos
+    and sin are multiplied by 0.1 ln(factor) + 1."""
+    rotary_dim: int
+    base: float
+    scaling: Optional[Mapping[str, float]] = None
+    kind: str = "rotary_half"
+
+
+@dataclass(frozen=True)
 class PositionSpec:
     """Rotary position encoding on the first `rotary_dim` dims of each head,
     pairs (i, i+1) (QStream src/engine.c:205-234 with head_dim -> rotary_dim)."""
@@ -88,6 +115,48 @@ class AttentionSpec:
 
 
 @dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Causal softmax attention whose keys and values are linear maps of one cached latent per token.
+
+    Queries: c_q = RMSnorm(W_dq h) (rank `q_rank`), q = W_uq c_q, per head [head_dim unrotated | rot_dim rotated].
+    W_dkv h gives the latent c (rank `kv_rank`, RMS-normed) and one rotated key part of `rot_dim` shared by all heads;
+    only these are cached.  Per head the unrotated key is W_uk c and the value W_uv c (`v_head_dim`).  The score is
+    (q_unrotated . k_unrotated + q_rotated . k_rotated) * `score_scale`.  `shares_cache`: the layer has no W_dkv and
+    reads the latents another layer cached, with its own W_uk, W_uv and queries."""
+    width: int
+    n_heads: int
+    head_dim: int
+    rot_dim: int
+    v_head_dim: int
+    q_rank: int
+    kv_rank: int
+    score_scale: float
+    eps: float
+    position: Optional[object] = None
+    shares_cache: bool = False
+    kind: str = "latent_attention"
+    names: Mapping[str, str] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class MlstmSpec:
+    """Matrix memory with exponential gates (the mLSTM of xLSTM): q = W_q h key_dim^-1/2, k = W_k h, v = W_v h per head,
+    log gates i = cap tanh((W_i h + b_i) / cap), f = logsigmoid(cap tanh((W_f h + b_f) / cap)) (`gate_cap` 0: no cap);
+    m_t = max(f + m_{t-1}, i) with m_0 = 0; S_t = exp(f + m_{t-1} - m_t) S_{t-1} + exp(i - m_t) k v^T, n_t likewise with
+    k alone; o = S_t^T q / (max(|n_t . q|, exp(-m_t)) + 1e-6); each head's o divided by its root mean square, times a
+    weight, times sigmoid(W_g h), then W_o.  State per sequence in 32-bit: S and n ([heads, value_dim + 1, key_dim])
+    and m ([heads])."""
+    width: int
+    n_heads: int
+    key_dim: int
+    value_dim: int
+    gate_cap: float
+    eps: float
+    kind: str = "mlstm"
+    names: Mapping[str, str] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
 class DecayAttentionSpec:
     """Linear attention with a fixed decay per head: S_t = decay_h S_{t-1} + k_t v_t^T, o_t = S_t^T q_t, with
     `activation` on q, k and v; the concatenated heads get one RMS norm (plain weight), a sigmoid gate from
@@ -132,11 +201,34 @@ class MlpSpec:
 
 @dataclass(frozen=True)
 class GatedMlpSpec:
-    """Gated feed-forward without biases: down(act(gate h) * (up h))."""
+    """Gated feed-forward: down(act(gate h) * (up h)), every projection with a bias if `bias`."""
     width: int
     inner: int
     activation: str = "silu"
     kind: str = "gated_mlp"
+    names: Mapping[str, str] = field(default_factory=dict)
+    bias: bool = False
+
+
+@dataclass(frozen=True)
+class RoutedExpertsSpec:
+    """A mixture of `n_experts` small feed-forward layers W_down act(W_up h) without biases, of which a token uses `top`.
+
+    Router: scores s = sigmoid(W_router h) in 32-bit; choice scores s + correction; the experts form `groups` equal
+    groups of neighbours, a group's score is the sum of its two largest choice scores, and only experts of the best
+    `keep` groups can be chosen; the `top` largest choice scores win; their weights are s * `route_scale`, not
+    renormalised.  `shared_inner` > 0: one more expert of that size runs for every token and is added, multiplied by
+    sigmoid(w_sg . h)."""
+    width: int
+    n_experts: int
+    inner: int
+    top: int
+    groups: int = 1
+    keep: int = 1
+    route_scale: float = 1.0
+    activation: str = "relu2"
+    shared_inner: int = 0
+    kind: str = "routed_experts"
     names: Mapping[str, str] = field(default_factory=dict)
 
 
@@ -150,6 +242,9 @@ class BlockSpec:
     arrangement "scaled_residual": the same with x kept in 32-bit whatever the engine's type and
         every branch multiplied by `residual_scale`: x += m mixer(norm_1(x)); x += m ffn(norm_2(x));
         `ffn` may be None (then only "input" is needed).
+    arrangement "sandwich": a norm before and after each sublayer, x in 32-bit:
+        x += norm_1b(mixer(norm_1(x))); x += norm_2b(ffn(norm_2(x)))
+                                        (norms: "input", "post_input", and with a feed-forward "post_mixer", "post_ffn")
     """
     mixer: object
     ffn: object
@@ -189,6 +284,19 @@ class PairEmbeddingSpec:
     mul_cur: int = 0
     stream_dtype: Optional[str] = None
     kind: str = "pair_embedding"
+    names: Mapping[str, str] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class NormedEmbeddingSpec:
+    """x = norm(table[token]): the token's row followed by a norm with a weight and no bias (layer norm if `center`,
+    else RMS), delivered in `stream_dtype` ("float32": a 32-bit residual stream; None: the engine's type)."""
+    vocab_size: int
+    width: int
+    eps: float
+    center: bool = True
+    stream_dtype: Optional[str] = None
+    kind: str = "normed_embedding"
     names: Mapping[str, str] = field(default_factory=dict)
 
 

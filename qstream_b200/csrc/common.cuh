@@ -16,7 +16,7 @@
 enum QsDtype { QS_F32 = 0, QS_BF16 = 1 };
 
 enum QsActivation { QS_ACT_NONE = 0, QS_ACT_GELU_TANH = 1, QS_ACT_GELU_ERF = 2, QS_ACT_SILU = 3, QS_ACT_SIGMOID = 4,
-                    QS_ACT_TANH = 5 };
+                    QS_ACT_TANH = 5, QS_ACT_RELU2 = 6 };
 
 // Codes follow QsError in errors.py (QStream include/qsf/error.h:14-32).
 enum { QS_OK = 0, QS_ERR_INVALID_INPUT = 11, QS_ERR_INTERNAL = 15 };
@@ -148,6 +148,7 @@ __device__ __forceinline__ float apply_activation(float v, int act) {
     if (act == QS_ACT_SILU) return silu_f32(v);
     if (act == QS_ACT_SIGMOID) return sigmoid_f32(v);
     if (act == QS_ACT_TANH) return tanhf(v);
+    if (act == QS_ACT_RELU2) { const float r = fmaxf(v, 0.f); return r * r; }      // the square of relu
     return v;
 }
 

@@ -1,0 +1,281 @@
+// Routed experts: the router's choice, and the two ways the chosen experts run.
+//
+//   moe_route     per token: scores s = sigmoid(z); choice scores s + correction; experts in equal groups of
+//                 neighbours, a group's score the sum of its two largest choice scores, only the best `keep` groups
+//                 stay (the others count as minus infinity); the `top` largest choice scores win (equal scores: the
+//                 lower index); weights s * scale of the winners, not renormalised; optionally sigmoid of one more
+//                 logit per token (the gate of a shared expert)
+//   few tokens    moe_expert_up / moe_expert_down: every (token, chosen expert) pair reads its expert's matrices
+//                 through the routing table on the device, so a step can be captured and replayed
+//   many tokens   moe_sort orders the pairs by expert; the caller runs one matrix product per expert over its rows
+//                 and moe_combine adds each token's weighted results
+//
+// Router arithmetic, weights and all sums are 32-bit; a token's sum runs over its experts in the order of choice.
+#include "common.cuh"
+
+namespace {
+
+constexpr int MAX_EXPERTS = 1024;
+
+// One warp per token.  Lanes compute the scores; lane 0 selects.
+__global__ void moe_route_kernel(int32_t* __restrict__ idx, float* __restrict__ wts, float* __restrict__ shared_gate,
+                                 const float* __restrict__ z, size_t ldz, const void* __restrict__ corr, int corr_dtype,
+                                 int T, int E, int top, int groups, int keep, float scale, int gate_col) {
+    extern __shared__ float sm[];                       // per warp: s [E], choice [E], group score [groups]
+    grid_dep_launch();
+    grid_dep_wait();
+    const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * warps + warp;
+    if (t >= T) return;
+    float* s = sm + (size_t)warp * (2 * E + groups);
+    float* choice = s + E;
+    float* gscore = choice + E;
+    const float* zr = z + (size_t)t * ldz;
+    for (int e = lane; e < E; e += 32) {
+        s[e] = sigmoid_f32(zr[e]);
+        choice[e] = s[e] + (corr ? load_as_f32(corr, corr_dtype, e) : 0.f);
+    }
+    if (shared_gate && lane == 0 && gate_col >= 0) shared_gate[t] = sigmoid_f32(zr[gate_col]);
+    __syncwarp();
+    const int per = E / groups;
+    if (keep < groups) {
+        for (int g = lane; g < groups; g += 32) {
+            float a = -INFINITY, b = -INFINITY;          // the two largest
+            for (int e = g * per; e < (g + 1) * per; ++e) {
+                const float c = choice[e];
+                if (c > a) { b = a; a = c; } else if (c > b) b = c;
+            }
+            gscore[g] = per > 1 ? a + b : a;
+        }
+        __syncwarp();
+        if (lane == 0) {
+            // keep the best `keep` groups: drop the others' experts
+            for (int n = 0; n < groups - keep; ++n) {
+                int worst = -1;
+                for (int g = 0; g < groups; ++g)            // the lowest score; among equals the highest index goes
+                    if (gscore[g] != INFINITY && (worst < 0 || gscore[g] <= gscore[worst])) worst = g;
+                gscore[worst] = INFINITY;                   // marks a dropped group
+                for (int e = worst * per; e < (worst + 1) * per; ++e) choice[e] = -INFINITY;
+            }
+        }
+        __syncwarp();
+    }
+    if (lane == 0) {
+        for (int j = 0; j < top; ++j) {
+            int best = -1;
+            for (int e = 0; e < E; ++e)
+                if (choice[e] != -INFINITY && (best < 0 || choice[e] > choice[best])) best = e;
+            if (best < 0) best = 0;                         // fewer live experts than `top`: cannot happen with a sound config
+            idx[(size_t)t * top + j] = best;
+            wts[(size_t)t * top + j] = s[best] * scale;
+            choice[best] = -INFINITY;
+        }
+    }
+}
+
+// hidden[pair, f] = act(W_up[e][f, :] . h[token, :]) for pair = token * top + j, e = idx[pair]: a block stages the
+// token's row in shared memory as 32-bit floats, a warp takes one hidden unit at a time.
+template <typename T>
+__global__ void moe_expert_up_kernel(T* __restrict__ hidden, size_t ldh, const T* __restrict__ x, size_t ldx,
+                                     const T* __restrict__ w_up, const int32_t* __restrict__ idx,
+                                     const int32_t* __restrict__ tok_slot, int top, int D, int F, int rows_per_block, int act) {
+    extern __shared__ float xs[];
+    grid_dep_launch();
+    grid_dep_wait();
+    const int pair = blockIdx.x, t = pair / top;
+    const int f0 = blockIdx.y * rows_per_block;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    if (tok_slot[t] < 0) {
+        for (int f = f0 + threadIdx.x; f < min(F, f0 + rows_per_block); f += blockDim.x) hidden[(size_t)pair * ldh + f] = from_f32<T>(0.f);
+        return;
+    }
+    for (int i = threadIdx.x; i < D; i += blockDim.x) xs[i] = to_f32(x[(size_t)t * ldx + i]);
+    __syncthreads();
+    const T* w = w_up + (size_t)idx[pair] * F * D;
+    for (int f = f0 + warp; f < min(F, f0 + rows_per_block); f += warps) {
+        const T* wr = w + (size_t)f * D;
+        float acc = 0.f;
+        for (int i = lane; i < D; i += 32) acc = fmaf(to_f32(wr[i]), xs[i], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) hidden[(size_t)pair * ldh + f] = from_f32<T>(apply_activation(acc, act));
+    }
+}
+
+// out[t, d] = sum_j wts[t, j] * (W_down[idx[t, j]][d, :] . hidden[t * top + j, :])  (+ add[t, d] * add_scale[t]),
+// 32-bit.  A block stages the token's `top` hidden rows; a warp takes one output element at a time.
+template <typename T>
+__global__ void moe_expert_down_kernel(float* __restrict__ out, size_t ldo, const T* __restrict__ hidden, size_t ldh,
+                                       const T* __restrict__ w_down, const int32_t* __restrict__ idx,
+                                       const float* __restrict__ wts, const int32_t* __restrict__ tok_slot,
+                                       const void* __restrict__ add, int add_dtype, size_t ldadd,
+                                       const float* __restrict__ add_scale, int top, int D, int F, int rows_per_block) {
+    extern __shared__ float hs[];                       // [top][F]
+    grid_dep_launch();
+    grid_dep_wait();
+    const int t = blockIdx.x;
+    const int d0 = blockIdx.y * rows_per_block;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    if (tok_slot[t] < 0) {
+        for (int d = d0 + threadIdx.x; d < min(D, d0 + rows_per_block); d += blockDim.x) out[(size_t)t * ldo + d] = 0.f;
+        return;
+    }
+    for (int i = threadIdx.x; i < top * F; i += blockDim.x) {
+        const int j = i / F;
+        hs[i] = to_f32(hidden[((size_t)t * top + j) * ldh + (i - j * F)]);
+    }
+    __syncthreads();
+    for (int d = d0 + warp; d < min(D, d0 + rows_per_block); d += warps) {
+        float total = 0.f;
+        for (int j = 0; j < top; ++j) {
+            const T* wr = w_down + ((size_t)idx[(size_t)t * top + j] * D + d) * F;
+            float acc = 0.f;
+            for (int i = lane; i < F; i += 32) acc = fmaf(to_f32(wr[i]), hs[j * F + i], acc);
+            total = fmaf(wts[(size_t)t * top + j], warp_sum(acc), total);
+        }
+        if (lane == 0) {
+            if (add) total = fmaf(load_as_f32(add, add_dtype, (size_t)t * ldadd + d), add_scale ? add_scale[t] : 1.0f, total);
+            out[(size_t)t * ldo + d] = total;
+        }
+    }
+}
+
+// The (token, choice) pairs ordered by expert, by one block: offsets[e] .. offsets[e + 1] are expert e's places,
+// place_token[p] the token whose row goes there, pair_place[pair] the place of a pair.  Pairs of padding rows
+// (slot < 0) are counted for the expert they name: their rows are zeros and nobody reads their results.
+__global__ void moe_sort_kernel(int32_t* __restrict__ offsets, int32_t* __restrict__ place_token,
+                                int32_t* __restrict__ pair_place, const int32_t* __restrict__ idx, int n_pairs, int top, int E) {
+    __shared__ int count[MAX_EXPERTS + 1];
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) count[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) atomicAdd(&count[idx[p]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < E; ++e) { const int c = count[e]; offsets[e] = run; count[e] = run; run += c; }
+        offsets[E] = run;
+    }
+    __syncthreads();
+    // places inside an expert's range in the order of the pairs: a token's result does not depend on its place,
+    // but a fixed order keeps runs alike
+    for (int base = 0; base < n_pairs; base += blockDim.x) {
+        const int p = base + threadIdx.x;
+        const int e = p < n_pairs ? idx[p] : -1;
+        for (int turn = 0; turn < (int)blockDim.x; turn += 32) {       // warps take turns, lanes in order
+            if ((int)(threadIdx.x & ~31u) == turn && e >= 0) {
+                const unsigned live = __activemask();
+                const unsigned same = __match_any_sync(live, e);
+                const int rank = __popc(same & ((1u << (threadIdx.x & 31)) - 1));
+                const int first = __shfl_sync(same, count[e], __ffs(same) - 1);
+                const int place = first + rank;
+                place_token[place] = p / top;
+                pair_place[p] = place;
+                if (rank == __popc(same) - 1) count[e] = place + 1;
+            }
+            __syncthreads();
+        }
+    }
+}
+
+// out[t, :] = sum_j wts[t, j] * y[pair_place[t * top + j], :]  (+ add[t, :] * add_scale[t]), in 32-bit.
+template <typename TY>
+__global__ void moe_combine_kernel(float* __restrict__ out, size_t ldo, const TY* __restrict__ y, size_t ldy,
+                                   const int32_t* __restrict__ pair_place, const float* __restrict__ wts,
+                                   const int32_t* __restrict__ tok_slot, const void* __restrict__ add, int add_dtype,
+                                   size_t ldadd, const float* __restrict__ add_scale, int top, int D) {
+    grid_dep_launch();
+    grid_dep_wait();
+    const size_t t = blockIdx.x;
+    const bool live = tok_slot[t] >= 0;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float total = 0.f;
+        if (live) {
+            for (int j = 0; j < top; ++j)
+                total = fmaf(wts[t * top + j], to_f32(y[(size_t)pair_place[t * top + j] * ldy + d]), total);
+            if (add) total = fmaf(load_as_f32(add, add_dtype, t * ldadd + d), add_scale ? add_scale[t] : 1.0f, total);
+        }
+        out[t * ldo + d] = total;
+    }
+}
+
+}  // namespace
+
+QS_API int qs_moe_route(int32_t* idx, float* wts, float* shared_gate, const float* z, long long ldz, const void* corr,
+                        int corr_dtype, int T, int E, int top, int groups, int keep, float scale, int gate_col,
+                        cudaStream_t stream) {
+    if (T == 0) return QS_OK;
+    QS_REQUIRE(T > 0 && E > 0 && E <= MAX_EXPERTS && top > 0 && top <= E, "moe_route: bad sizes T=%d E=%d top=%d", T, E, top);
+    QS_REQUIRE(groups > 0 && E % groups == 0 && keep > 0 && keep <= groups, "moe_route: %d experts in %d groups, %d kept", E, groups, keep);
+    QS_REQUIRE(keep * (E / groups) >= top, "moe_route: %d kept groups of %d experts cannot give %d choices", keep, E / groups, top);
+    const int warps = 4;
+    const size_t smem = (size_t)warps * (2 * E + groups) * sizeof(float);
+    cudaError_t e = qs_launch_dependent(moe_route_kernel, dim3((T + warps - 1) / warps), dim3(warps * 32), smem, stream, idx, wts,
+                                        shared_gate, z, (size_t)ldz, corr, corr_dtype, T, E, top, groups, keep, scale, gate_col);
+    if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "moe_route: %s", cudaGetErrorString(e));
+    return qs_check_launch("moe_route");
+}
+
+QS_API int qs_moe_expert_up(void* hidden, long long ldh, const void* x, long long ldx, const void* w_up, int dtype,
+                            const int32_t* idx, const int32_t* tok_slot, int T, int top, int D, int F, int act,
+                            cudaStream_t stream) {
+    if (T == 0) return QS_OK;
+    QS_REQUIRE(T > 0 && top > 0 && D > 0 && F > 0, "moe_expert_up: bad sizes");
+    QS_REQUIRE((size_t)D * sizeof(float) <= 200 * 1024, "moe_expert_up: width %d does not fit shared memory", D);
+    const int rows_per_block = 64;
+    const size_t smem = (size_t)D * sizeof(float);
+    dim3 grid(T * top, (F + rows_per_block - 1) / rows_per_block);
+    cudaError_t e = cudaSuccess;
+#define GO(TT) do { if (smem > 48 * 1024) e = cudaFuncSetAttribute(moe_expert_up_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    if (e == cudaSuccess) e = qs_launch_dependent(moe_expert_up_kernel<TT>, grid, dim3(256), smem, stream, (TT*)hidden, (size_t)ldh, (const TT*)x, \
+        (size_t)ldx, (const TT*)w_up, idx, tok_slot, top, D, F, rows_per_block, act); } while (0)
+    if (dtype == QS_F32) GO(float);
+    else if (dtype == QS_BF16) GO(__nv_bfloat16);
+    else return qs_fail(QS_ERR_INVALID_INPUT, "moe_expert_up: unknown dtype %d", dtype);
+#undef GO
+    if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "moe_expert_up: %s", cudaGetErrorString(e));
+    return qs_check_launch("moe_expert_up");
+}
+
+QS_API int qs_moe_expert_down(float* out, long long ldo, const void* hidden, long long ldh, const void* w_down, int dtype,
+                              const int32_t* idx, const float* wts, const int32_t* tok_slot, const void* add, int add_dtype,
+                              long long ldadd, const float* add_scale, int T, int top, int D, int F, cudaStream_t stream) {
+    if (T == 0) return QS_OK;
+    QS_REQUIRE(T > 0 && top > 0 && D > 0 && F > 0, "moe_expert_down: bad sizes");
+    const size_t smem = (size_t)top * F * sizeof(float);
+    QS_REQUIRE(smem <= 200 * 1024, "moe_expert_down: %d x %d hidden values do not fit shared memory", top, F);
+    const int rows_per_block = 64;
+    dim3 grid(T, (D + rows_per_block - 1) / rows_per_block);
+    cudaError_t e = cudaSuccess;
+#define GO(TT) do { if (smem > 48 * 1024) e = cudaFuncSetAttribute(moe_expert_down_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    if (e == cudaSuccess) e = qs_launch_dependent(moe_expert_down_kernel<TT>, grid, dim3(256), smem, stream, out, (size_t)ldo, (const TT*)hidden, \
+        (size_t)ldh, (const TT*)w_down, idx, wts, tok_slot, add, add_dtype, (size_t)ldadd, add_scale, top, D, F, rows_per_block); } while (0)
+    if (dtype == QS_F32) GO(float);
+    else if (dtype == QS_BF16) GO(__nv_bfloat16);
+    else return qs_fail(QS_ERR_INVALID_INPUT, "moe_expert_down: unknown dtype %d", dtype);
+#undef GO
+    if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "moe_expert_down: %s", cudaGetErrorString(e));
+    return qs_check_launch("moe_expert_down");
+}
+
+QS_API int qs_moe_sort(int32_t* offsets, int32_t* place_token, int32_t* pair_place, const int32_t* idx, int n_pairs,
+                       int top, int E, cudaStream_t stream) {
+    QS_REQUIRE(n_pairs > 0 && top > 0 && E > 0 && E <= MAX_EXPERTS, "moe_sort: bad sizes");
+    moe_sort_kernel<<<1, 1024, 0, stream>>>(offsets, place_token, pair_place, idx, n_pairs, top, E);
+    return qs_check_launch("moe_sort");
+}
+
+QS_API int qs_moe_combine(float* out, long long ldo, const void* y, int y_dtype, long long ldy, const int32_t* pair_place,
+                          const float* wts, const int32_t* tok_slot, const void* add, int add_dtype, long long ldadd,
+                          const float* add_scale, int T, int top, int D, cudaStream_t stream) {
+    if (T == 0) return QS_OK;
+    QS_REQUIRE(T > 0 && top > 0 && D > 0, "moe_combine: bad sizes");
+    const int threads = D >= 1024 ? 256 : 128;
+    cudaError_t e;
+#define GO(TY) e = qs_launch_dependent(moe_combine_kernel<TY>, dim3(T), dim3(threads), 0, stream, out, (size_t)ldo, (const TY*)y, \
+        (size_t)ldy, pair_place, wts, tok_slot, add, add_dtype, (size_t)ldadd, add_scale, top, D)
+    if (y_dtype == QS_F32) GO(float);
+    else if (y_dtype == QS_BF16) GO(__nv_bfloat16);
+    else return qs_fail(QS_ERR_INVALID_INPUT, "moe_combine: unknown dtype %d", y_dtype);
+#undef GO
+    if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "moe_combine: %s", cudaGetErrorString(e));
+    return qs_check_launch("moe_combine");
+}

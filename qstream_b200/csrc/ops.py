@@ -16,9 +16,9 @@ from ..errors import QsError, QStreamError
 from . import build as _build
 
 F32, BF16 = 0, 1
-ACT_NONE, ACT_GELU_TANH, ACT_GELU_ERF, ACT_SILU, ACT_SIGMOID, ACT_TANH = 0, 1, 2, 3, 4, 5
+ACT_NONE, ACT_GELU_TANH, ACT_GELU_ERF, ACT_SILU, ACT_SIGMOID, ACT_TANH, ACT_RELU2 = 0, 1, 2, 3, 4, 5, 6
 ACTIVATIONS = {None: ACT_NONE, "none": ACT_NONE, "gelu_new": ACT_GELU_TANH, "gelu": ACT_GELU_ERF,
-               "silu": ACT_SILU, "sigmoid": ACT_SIGMOID, "tanh": ACT_TANH}
+               "silu": ACT_SILU, "sigmoid": ACT_SIGMOID, "tanh": ACT_TANH, "relu2": ACT_RELU2}
 
 _lib = None
 
@@ -49,7 +49,27 @@ _SIGNATURES = {
     "qs_state_scan": ([c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int,
                        c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int,
                        c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-                       c_void_p], c_int),
+                       c_void_p, c_void_p, c_longlong, c_float, c_void_p], c_int),
+    "qs_mlstm_gates": ([c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_float, c_void_p, c_longlong,
+                        c_void_p, c_void_p, c_int, c_int, c_int, c_void_p], c_int),
+    "qs_mlstm_output": ([c_void_p, c_int, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int,
+                         c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_float, c_void_p], c_int),
+    "qs_branch_norm": ([c_void_p, c_int, c_longlong, c_void_p, c_int, c_longlong, c_void_p, c_int, c_longlong, c_void_p,
+                        c_int, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p], c_int),
+    "qs_latent_prepare": ([c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p, c_longlong,
+                           c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_float, c_int, c_void_p, c_void_p,
+                           c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p], c_int),
+    "qs_latent_q_rotate": ([c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int,
+                            c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p], c_int),
+    "qs_moe_route": ([c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                      c_int, c_float, c_int, c_void_p], c_int),
+    "qs_moe_expert_up": ([c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+                          c_int, c_int, c_int, c_void_p], c_int),
+    "qs_moe_expert_down": ([c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                            c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p], c_int),
+    "qs_moe_sort": ([c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p], c_int),
+    "qs_moe_combine": ([c_void_p, c_longlong, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                        c_longlong, c_void_p, c_int, c_int, c_int, c_void_p], c_int),
     "qs_token_shift": ([c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_longlong,
                         c_void_p, c_void_p, c_int, c_int, c_int, c_void_p], c_int),
     "qs_argmax": ([c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p], c_int),
@@ -364,11 +384,14 @@ def keep_last_rows(dst: torch.Tensor, src: torch.Tensor, seq_start, seq_slot, n_
 
 
 def state_scan(mode: str, q, k, v, state, seq_start, seq_slot, n_seq, n_heads, key_dim, value_dim, head_decay=None,
-               decay_logits=None, bonus=None, in_activation=None, chunks=None) -> torch.Tensor:
+               decay_logits=None, bonus=None, in_activation=None, chunks=None, token_decay=None, token_weight=None,
+               q_scale: float = 1.0) -> torch.Tensor:
     """Walk each sequence's tokens of this step through a per-head matrix state (float32 [slots, heads, value_dim,
     key_dim], updated in place); returns o [T, heads * value_dim] in float32.
     mode "decay": S <- decay_h S + k v^T, o = S^T q.  mode "wkv": o = (S + diag(bonus) k v^T)^T q, then
-    S <- diag(exp(-exp(decay_logits))) S + k v^T.
+    S <- diag(exp(-exp(decay_logits))) S + k v^T.  mode "gated": S <- a_t S + b_t k v^T, o = S^T (q q_scale) with
+    a = `token_decay`, b = `token_weight` (float32 [T, heads]); here `value_dim` counts one column more than v holds:
+    a column of ones, whose state is the normaliser n <- a_t n + b_t k and whose output n.q is each head's last element.
     `chunks` = (chunk_start, chunk_ids, seq_chunk, n_chunks), int32 device tensors: every sequence of the step cut
     into consecutive chunks (rows chunk_start[c] .. chunk_start[c + 1] of the packed batch; sequence s owns chunks
     seq_chunk[s] .. seq_chunk[s + 1]; chunk_ids = 0 .. n_chunks - 1).  The chunks then run side by side and a
@@ -383,13 +406,150 @@ def state_scan(mode: str, q, k, v, state, seq_start, seq_slot, n_seq, n_heads, k
         chunk_start, chunk_ids, seq_chunk, n_chunks = chunks
         chunk_state = torch.empty((n_chunks, n_heads * value_dim * key_dim), dtype=torch.float32, device=q.device)
         chunk_decay = torch.empty((n_chunks, n_heads * key_dim), dtype=torch.float32, device=q.device)
+    if mode == "gated" and (token_decay.dtype != torch.float32 or token_decay.stride() != token_weight.stride()):
+        raise QStreamError(QsError.INVALID_INPUT, "state_scan: the tokens' decays and weights must be float32 of one layout")
     check(library().qs_state_scan(
-        1 if mode == "wkv" else 0, ptr(o), o.stride(0), ptr(q), q.stride(0), ptr(k), k.stride(0), ptr(v), v.stride(0),
+        {"decay": 0, "wkv": 1, "gated": 2}[mode], ptr(o), o.stride(0), ptr(q), q.stride(0), ptr(k), k.stride(0), ptr(v), v.stride(0),
         dtype_code(q), ptr(decay_logits), decay_logits.stride(0) if decay_logits is not None else 0, ptr(head_decay),
         ptr(bonus), _code(bonus), ptr(state), state.stride(0), _int32(seq_start, "seq_start"),
         _int32(seq_slot, "seq_slot"), int(n_seq), T, n_heads, key_dim, value_dim, ACTIVATIONS[in_activation],
-        ptr(chunk_start), ptr(chunk_ids), int(n_chunks), ptr(seq_chunk), ptr(chunk_state), ptr(chunk_decay), stream()))
+        ptr(chunk_start), ptr(chunk_ids), int(n_chunks), ptr(seq_chunk), ptr(chunk_state), ptr(chunk_decay),
+        ptr(token_decay), ptr(token_weight), token_decay.stride(0) if token_decay is not None else 0, float(q_scale), stream()))
     return o
+
+
+def mlstm_gates(raw, cap: float, m_state, seq_start, seq_slot, n_seq: int, n_heads: int):
+    """The mLSTM's exponential gates as factors of its recurrence.  raw float32 [T, 2 heads] = (input | forget gate
+    projections, bias included); log gates i = cap tanh(. / cap), f = logsigmoid(cap tanh(. / cap)); with the running
+    maximum m (float32 [slots, heads], 0 for an empty sequence, updated in place): m_t = max(f + m_{t-1}, i),
+    a_t = exp(f + m_{t-1} - m_t), b_t = exp(i - m_t).  Returns (a, b, m), each float32 [T, heads]."""
+    T = raw.shape[0]
+    if raw.dtype != torch.float32 or raw.shape[1] != 2 * n_heads or raw.stride(1) != 1 or m_state.dtype != torch.float32:
+        raise QStreamError(QsError.INVALID_INPUT, "mlstm_gates: float32 [T, 2 heads] gates and a float32 state")
+    abm = torch.empty((3, T, n_heads), dtype=torch.float32, device=raw.device)
+    check(library().qs_mlstm_gates(ptr(abm[0]), ptr(abm[1]), ptr(abm[2]), n_heads, ptr(raw), raw.stride(0), float(cap),
+                                   ptr(m_state), m_state.stride(0), _int32(seq_start, "seq_start"),
+                                   _int32(seq_slot, "seq_slot"), int(n_seq), T, n_heads, stream()))
+    return abm[0], abm[1], abm[2]
+
+
+def mlstm_output(o, m, weight, gate, n_heads: int, value_dim: int, eps: float, out_dtype) -> torch.Tensor:
+    """From the gated scan's o [T, heads * (value_dim + 1)] (each head's last element the normaliser's product n.q) and
+    the running maxima m [T, heads]: y = o / (max(|n.q|, exp(-m)) + 1e-6), each head divided by its root mean square,
+    times weight, times sigmoid(gate) -> [T, heads * value_dim]."""
+    rows, _, ldi = _rows(o)
+    _, n, ldgate = _rows(gate)
+    out = torch.empty((rows, n_heads * value_dim), dtype=out_dtype, device=o.device)
+    check(library().qs_mlstm_output(ptr(out), dtype_code(out), out.stride(0), ptr(o), ldi, ptr(m), m.stride(0), ptr(weight),
+                                    dtype_code(weight), ptr(gate), dtype_code(gate), ldgate, rows, n_heads, value_dim,
+                                    float(eps), stream()))
+    return out
+
+
+def branch_norm(x, weight, eps: float, center: bool, out_dtype=None, branch=None, branch_weight=None, want_norm=True,
+                in_place=False):
+    """With `branch`: x <- x + norm(branch) * branch_weight (in place; without a weight the plain sum).  With
+    `want_norm`: returns h = norm(x) * weight in `out_dtype` (`in_place`: written over x).  norm is the layer norm
+    without bias (`center`) or the RMS norm, statistics in 32-bit, eps inside the root."""
+    rows, D, ldx = _rows(x)
+    h = None
+    if want_norm:
+        if weight is None or weight.numel() != D:
+            raise QStreamError(QsError.INVALID_INPUT, f"norm: width {D} but weight {None if weight is None else tuple(weight.shape)}")
+        h = x if in_place else torch.empty((rows, D), dtype=out_dtype or x.dtype, device=x.device)
+    ldy = 0
+    if branch is not None:
+        r2, D2, ldy = _rows(branch)
+        if (r2, D2) != (rows, D) or (branch_weight is not None and branch_weight.numel() != D):
+            raise QStreamError(QsError.INVALID_INPUT, "norm: the branch differs from x in shape")
+    check(library().qs_branch_norm(ptr(h), _code(h), h.stride(0) if h is not None else 0, ptr(x), dtype_code(x), ldx,
+                                   ptr(branch), _code(branch), ldy, ptr(branch_weight) if branch is not None else None,
+                                   _code(branch_weight), ptr(weight) if want_norm else None,
+                                   _code(weight) if want_norm else 0, rows, D, float(eps), int(bool(center)), stream()))
+    return h
+
+
+def latent_prepare(dq, q_norm, q_rank, dkv, kv_norm, kv_rank, rot_dim, rot_dims, freq, mag, eps, tok_slot, tok_pos,
+                   page_table, page_tokens, k_cache, v_cache, status):
+    """RMS norm of the query latent dq [T, q_rank] -> returned; RMS norm of the key latent dkv[:, :kv_rank] and the
+    rotation (rotate-half pairs, `freq` float64 [rot_dims / 2], cos and sin times `mag`) of dkv[:, kv_rank:], written
+    into the cache entry as keys [c | rotated part] and values c.  dkv None: a layer that reads another's cache."""
+    ref = dq if dq is not None else dkv
+    T = ref.shape[0]
+    cq = torch.empty((T, q_rank), dtype=dq.dtype, device=dq.device) if dq is not None else None
+    check(library().qs_latent_prepare(
+        ptr(cq), cq.stride(0) if cq is not None else 0, ptr(dq), dq.stride(0) if dq is not None else 0, ptr(q_norm),
+        _code(q_norm), int(q_rank), ptr(dkv), dkv.stride(0) if dkv is not None else 0, ptr(kv_norm), _code(kv_norm),
+        int(kv_rank), int(rot_dim), int(rot_dims), ptr(freq), float(mag), float(eps), dtype_code(ref),
+        _int32(tok_slot, "tok_slot"), _int32(tok_pos, "tok_pos"),
+        _int32(page_table, "page_table") if dkv is not None else None, page_table.shape[1] if dkv is not None else 0,
+        int(page_tokens), ptr(k_cache) if dkv is not None else None, ptr(v_cache) if dkv is not None else None, T,
+        ptr(status), stream()))
+    return cq
+
+
+def latent_q_rotate(q_abs, q, n_heads, dim, rot_dim, kv_rank, rot_dims, freq, mag, tok_slot, tok_pos) -> None:
+    """q [T, heads * (dim + rot_dim)]: every head's last rot_dim elements, rotated, go to q_abs
+    [T, heads * (kv_rank + rot_dim)] behind the head's first kv_rank elements."""
+    check(library().qs_latent_q_rotate(ptr(q_abs), q_abs.stride(0), ptr(q), q.stride(0), dtype_code(q), int(n_heads),
+                                       int(dim), int(rot_dim), int(kv_rank), int(rot_dims), ptr(freq), float(mag),
+                                       _int32(tok_slot, "tok_slot"), _int32(tok_pos, "tok_pos"), q.shape[0], stream()))
+
+
+# ------------------------------------------------------------------------------- routed experts
+
+def moe_route(z, correction, n_experts, top, groups, keep, scale, gate_col=-1):
+    """z float32 [T, >= n_experts] router logits.  Returns (idx int32 [T, top], weights float32 [T, top], shared gate
+    float32 [T] = sigmoid(z[:, gate_col]) or None): see csrc/moe.cu for the rule."""
+    T = z.shape[0]
+    if z.dtype != torch.float32 or z.stride(1) != 1:
+        raise QStreamError(QsError.INVALID_INPUT, "moe_route: router logits must be float32 rows")
+    idx = torch.empty((T, top), dtype=torch.int32, device=z.device)
+    wts = torch.empty((T, top), dtype=torch.float32, device=z.device)
+    gate = torch.empty((T,), dtype=torch.float32, device=z.device) if gate_col >= 0 else None
+    check(library().qs_moe_route(ptr(idx), ptr(wts), ptr(gate), ptr(z), z.stride(0), ptr(correction), _code(correction), T,
+                                 int(n_experts), int(top), int(groups), int(keep), float(scale), int(gate_col), stream()))
+    return idx, wts, gate
+
+
+def moe_experts_indirect(x, w_up, w_down, idx, wts, tok_slot, activation, add=None, add_scale=None) -> torch.Tensor:
+    """sum_j wts[t, j] W_down[idx[t, j]] act(W_up[idx[t, j]] x[t]) (+ add[t] * add_scale[t]) in float32 [T, D]; every
+    pair finds its expert's matrices (w_up [E, F, D], w_down [E, D, F]) on the device: for steps of few tokens."""
+    T, D, ldx = _rows(x)
+    E, F, _ = w_up.shape
+    top = idx.shape[1]
+    if w_up.dtype != x.dtype or w_down.dtype != x.dtype or not w_up.is_contiguous() or not w_down.is_contiguous():
+        raise QStreamError(QsError.INVALID_INPUT, "experts: matrices and activations must share a type")
+    hidden = torch.empty((T * top, F), dtype=x.dtype, device=x.device)
+    out = torch.empty((T, D), dtype=torch.float32, device=x.device)
+    check(library().qs_moe_expert_up(ptr(hidden), F, ptr(x), ldx, ptr(w_up), dtype_code(x), _int32(idx, "idx"),
+                                     _int32(tok_slot, "tok_slot"), T, top, D, F, ACTIVATIONS[activation], stream()))
+    check(library().qs_moe_expert_down(ptr(out), D, ptr(hidden), F, ptr(w_down), dtype_code(x), _int32(idx, "idx"), ptr(wts),
+                                       _int32(tok_slot, "tok_slot"), ptr(add), _code(add),
+                                       add.stride(0) if add is not None else 0, ptr(add_scale), T, top, D, F, stream()))
+    return out
+
+
+def moe_sort(idx, n_experts: int):
+    """The (token, choice) pairs ordered by expert: (offsets int32 [E + 1], place_token int32 [pairs], pair_place int32
+    [pairs])."""
+    T, top = idx.shape
+    meta = torch.empty((n_experts + 1 + 2 * T * top,), dtype=torch.int32, device=idx.device)
+    offsets, place_token, pair_place = meta[:n_experts + 1], meta[n_experts + 1:n_experts + 1 + T * top], meta[n_experts + 1 + T * top:]
+    check(library().qs_moe_sort(ptr(offsets), ptr(place_token), ptr(pair_place), _int32(idx, "idx"), T * top, top,
+                                int(n_experts), stream()))
+    return offsets, place_token, pair_place
+
+
+def moe_combine(y, pair_place, wts, tok_slot, add=None, add_scale=None) -> torch.Tensor:
+    """out[t] = sum_j wts[t, j] y[pair_place[t, j]] (+ add[t] * add_scale[t]) in float32."""
+    _, D, ldy = _rows(y)
+    T, top = wts.shape
+    out = torch.empty((T, D), dtype=torch.float32, device=y.device)
+    check(library().qs_moe_combine(ptr(out), D, ptr(y), dtype_code(y), ldy, ptr(pair_place), ptr(wts),
+                                   _int32(tok_slot, "tok_slot"), ptr(add), _code(add), add.stride(0) if add is not None else 0,
+                                   ptr(add_scale), T, top, D, stream()))
+    return out
 
 
 def token_shift(h, mu, last_row, tok_slot, tok_pos) -> torch.Tensor:

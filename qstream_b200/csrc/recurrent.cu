@@ -4,6 +4,10 @@
 //       S_t = decay_h S_{t-1} + k_t v_t^T,   o_t = S_t^T q_t                   q, k [dk], v, o [dv], S [dk, dv]
 //   time mixing with a decay per token and key channel and a bonus for the current token ("wkv"):
 //       o_t = (S_{t-1} + diag(u) k_t v_t^T)^T r_t,   S_t = diag(w_t) S_{t-1} + k_t v_t^T,   w_t = exp(-exp(d_t))
+//   matrix memory with a decay and an input weight per token and head ("gated"; the mLSTM's recurrence once its
+//   gates are turned into the factors a_t, b_t by `mlstm_gates_kernel`):
+//       S_t = a_t S_{t-1} + b_t k_t v_t^T,   o_t = S_t^T (q_t * q_scale);   the last column of S has v = 1 and so
+//       carries the normaliser n_t = a_t n_{t-1} + b_t k_t, whose product with q arrives as the last element of o
 //
 // The state lives in 32-bit, per slot as [heads][dv][dk] (a column of S is contiguous), starts at zero and is
 // read at the start of a step and written back at its end; everything between the projections and the output is
@@ -30,7 +34,7 @@ __device__ __forceinline__ int row_of(int ks, int ks_log2, int r) { return 4 * (
 //          the chunk starts from and leaving the sequence's last state in its slot;
 // PHASE 3: every chunk adds to its tokens' o what the state it started from contributes, decayed up to each token.
 // For phases 1 and 3 a "sequence" of the kernel is a chunk and its "slot" the chunk's place in the scratch.
-template <typename TI, bool WKV, int PHASE>
+template <typename TI, int MODE, int PHASE>
 __global__ void __launch_bounds__(256, 2)
 state_scan_kernel(float* __restrict__ o, size_t ldo,
                   const TI* __restrict__ q, size_t ldq, const TI* __restrict__ k, size_t ldk,
@@ -38,7 +42,9 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
                   const float* __restrict__ head_decay, const void* __restrict__ bonus, int bonus_dtype,
                   float* __restrict__ state, size_t slot_stride,
                   const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot, int n_seq, int T_rows,
-                  int H, int dk, int dv, int ks_log2, int cols, int in_act, int vec) {
+                  int H, int dk, int dv, int ks_log2, int cols, int in_act, int vec,
+                  const float* __restrict__ ga, const float* __restrict__ gb, size_t ldg, float q_scale) {
+    constexpr bool WKV = MODE == 1, GATED = MODE == 2;
     extern __shared__ float smem[];
     const int KS = 1 << ks_log2, dkp = KS * RK;
     float* sq = smem;                                   // [TILE][dkp]
@@ -46,6 +52,8 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
     float* sw = sk + TILE * dkp;                        // [TILE][dkp]   (WKV only)
     float* sv = sw + (WKV ? TILE * dkp : 0);            // [TILE][cols]
     float* carry = sv + TILE * cols;                    // [dkp]         (PHASE 3: the decay from the chunk's start on)
+    float* sa = carry + dkp;                            // [TILE]        (GATED: the tokens' decays)
+    const int dvv = GATED ? dv - 1 : dv;                // columns that v holds per head: the gated form adds one of ones
     grid_dep_launch();
     grid_dep_wait();
     const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * cols;
@@ -90,7 +98,7 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
         for (int j = 0; j < 4; ++j)
             u[4 * r4 + j] = (WKV && PHASE != 3 && i + j < dk) ? load_as_f32(bonus, bonus_dtype, (size_t)h * dk + i + j) : 0.f;
     }
-    const float decay = WKV ? 0.f : head_decay[h];
+    const float decay = (WKV || GATED) ? 0.f : head_decay[h];
     if (PHASE == 3)
         for (int i = tid; i < dkp; i += blockDim.x) carry[i] = 1.0f;
 
@@ -102,7 +110,7 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
         for (int i = tid; i < dkp; i += blockDim.x) {
             // all of the tile's loads first, so that they are in flight together
             TI qraw[TILE], kraw[TILE];
-            float draw[TILE];
+            float draw[TILE];                           // GATED: b_t (phases 0, 1) or a_t (phase 3)
 #pragma unroll
             for (int tt = 0; tt < TILE; ++tt) {
                 if (tt < nt && i < dk) {
@@ -110,6 +118,7 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
                     qraw[tt] = q[row * ldq + h * dk + i];
                     if (PHASE != 3) kraw[tt] = k[row * ldk + h * dk + i];
                     if (WKV) draw[tt] = dlog[row * ldd + h * dk + i];
+                    if (GATED) draw[tt] = (PHASE == 3 ? ga : gb)[row * ldg + h];
                 }
             }
             float run = PHASE == 3 ? carry[i] : 1.0f;
@@ -121,9 +130,11 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
                         qv = apply_activation(to_f32(qraw[tt]), in_act);
                         if (PHASE != 3) kv = apply_activation(to_f32(kraw[tt]), in_act);
                         if (WKV) wv = expf(-expf(draw[tt]));
+                        if (GATED) { qv *= q_scale; if (PHASE != 3) kv *= draw[tt]; }
                     }
                     if (PHASE == 3) {
                         if (WKV) { qv *= run; run *= wv; }
+                        else if (GATED) { run *= (i < dk ? draw[tt] : 0.f); qv *= run; }
                         else { run *= decay; qv *= run; }
                     } else {
                         sk[tt * dkp + i] = kv;
@@ -134,11 +145,14 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
             }
             if (PHASE == 3) carry[i] = run;
         }
-        if (PHASE != 3)
+        if (PHASE != 3) {
             for (int e = tid; e < nt * cols; e += blockDim.x) {
                 const int tt = e / cols, c = e - tt * cols;
-                sv[e] = c < n_cols ? apply_activation(to_f32(v[(size_t)(base + tt) * ldv + h * dv + col0 + c]), in_act) : 0.f;
+                sv[e] = c >= n_cols ? 0.f : (GATED && col0 + c == dvv) ? 1.0f
+                        : apply_activation(to_f32(v[(size_t)(base + tt) * ldv + h * dvv + col0 + c]), in_act);
             }
+            if (GATED && tid < nt) sa[tid] = ga[(size_t)(base + tid) * ldg + h];
+        }
         __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {
             const float v0 = (PHASE == 3 || !own0) ? 0.f : sv[tt * cols + CPT * pair];
@@ -172,8 +186,9 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
                             S0[r] = fmaf(wa[j], S0[r], kv0);
                             S1[r] = fmaf(wa[j], S1[r], kv1);
                         } else {
-                            S0[r] = fmaf(decay, S0[r], kv0);
-                            S1[r] = fmaf(decay, S1[r], kv1);
+                            const float dec = GATED ? sa[tt] : decay;
+                            S0[r] = fmaf(dec, S0[r], kv0);
+                            S1[r] = fmaf(dec, S1[r], kv1);
                             acc0 = fmaf(qa[j], S0[r], acc0);
                             acc1 = fmaf(qa[j], S1[r], acc1);
                         }
@@ -215,7 +230,7 @@ state_scan_kernel(float* __restrict__ o, size_t ldo,
 // or decay_h ^ tokens for a fixed decay per head.  chunk_decay [chunks][H * dk].
 __global__ void chunk_decay_kernel(float* __restrict__ chunk_decay, const float* __restrict__ dlog, size_t ldd,
                                    const float* __restrict__ head_decay, const int32_t* __restrict__ chunk_start,
-                                   int n, int dk) {
+                                   int n, int dk, const float* __restrict__ ga, size_t ldg) {
     const int c = blockIdx.x;
     const int t0 = chunk_start[c], t1 = chunk_start[c + 1];
     for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < n; i += gridDim.y * blockDim.x) {
@@ -224,6 +239,9 @@ __global__ void chunk_decay_kernel(float* __restrict__ chunk_decay, const float*
             float sum = 0.f;
             for (int t = t0; t < t1; ++t) sum += expf(dlog[(size_t)t * ldd + i]);
             a = expf(-sum);
+        } else if (ga) {                                // a decay per token and head: their product in order
+            a = 1.0f;
+            for (int t = t0; t < t1; ++t) a *= ga[(size_t)t * ldg + i / dk];
         } else {
             a = 1.0f;
             const float d = head_decay[i / dk];
@@ -293,10 +311,12 @@ __global__ void token_shift_kernel(T* __restrict__ out, size_t ldo, size_t mix_s
 }
 
 template <typename TI>
-int launch_scan(bool wkv, int phase, float* o, long long ldo, const void* q, long long ldq, const void* k, long long ldk,
+int launch_scan(int mode, int phase, float* o, long long ldo, const void* q, long long ldq, const void* k, long long ldk,
                 const void* v, long long ldv, const float* dlog, long long ldd, const float* head_decay, const void* bonus,
                 int bonus_dtype, float* state, long long slot_stride, const int32_t* seq_start, const int32_t* seq_slot,
-                int n_seq, int T_rows, int H, int dk, int dv, int in_act, cudaStream_t stream) {
+                int n_seq, int T_rows, int H, int dk, int dv, int in_act, const float* ga, const float* gb, long long ldg,
+                float q_scale, cudaStream_t stream) {
+    const bool wkv = mode == 1;
     int ks_log2 = 0;
     while ((RK << ks_log2) < dk) ++ks_log2;
     const int KS = 1 << ks_log2;
@@ -306,24 +326,132 @@ int launch_scan(bool wkv, int phase, float* o, long long ldo, const void* q, lon
     while (cols > 8 * CPT && (long long)n_seq * H * ((dv + cols - 1) / cols) < 148 && cols / CPT * KS > 64) cols >>= 1;
     const int threads = ((cols / CPT * KS + 31) / 32) * 32;
     const int dkp = KS * RK;
-    const size_t smem = ((size_t)TILE * ((wkv ? 3 : 2) * dkp + cols) + dkp) * sizeof(float);
+    const size_t smem = ((size_t)TILE * ((wkv ? 3 : 2) * dkp + cols) + dkp + TILE) * sizeof(float);
     const int vec = dk % 4 == 0 && slot_stride % 4 == 0 && ((uintptr_t)state % 16) == 0;
     dim3 grid(n_seq, H, (dv + cols - 1) / cols);
     cudaError_t e;
-#define GO(WKV, PHASE) do { e = smem > 48 * 1024 ? cudaFuncSetAttribute(state_scan_kernel<TI, WKV, PHASE>, \
+#define GO(MODE, PHASE) do { e = smem > 48 * 1024 ? cudaFuncSetAttribute(state_scan_kernel<TI, MODE, PHASE>, \
             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) : cudaSuccess; \
-    if (e == cudaSuccess) e = qs_launch_dependent(state_scan_kernel<TI, WKV, PHASE>, grid, dim3(threads), smem, stream, o, (size_t)ldo, \
+    if (e == cudaSuccess) e = qs_launch_dependent(state_scan_kernel<TI, MODE, PHASE>, grid, dim3(threads), smem, stream, o, (size_t)ldo, \
         (const TI*)q, (size_t)ldq, (const TI*)k, (size_t)ldk, (const TI*)v, (size_t)ldv, dlog, (size_t)ldd, head_decay, bonus, \
-        bonus_dtype, state, (size_t)slot_stride, seq_start, seq_slot, n_seq, T_rows, H, dk, dv, ks_log2, cols, in_act, vec); } while (0)
-    if (wkv) { if (phase == 0) GO(true, 0); else if (phase == 1) GO(true, 1); else GO(true, 3); }
-    else { if (phase == 0) GO(false, 0); else if (phase == 1) GO(false, 1); else GO(false, 3); }
+        bonus_dtype, state, (size_t)slot_stride, seq_start, seq_slot, n_seq, T_rows, H, dk, dv, ks_log2, cols, in_act, vec, \
+        ga, gb, (size_t)ldg, q_scale); } while (0)
+    if (mode == 1) { if (phase == 0) GO(1, 0); else if (phase == 1) GO(1, 1); else GO(1, 3); }
+    else if (mode == 2) { if (phase == 0) GO(2, 0); else if (phase == 1) GO(2, 1); else GO(2, 3); }
+    else { if (phase == 0) GO(0, 0); else if (phase == 1) GO(0, 1); else GO(0, 3); }
 #undef GO
     if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "state_scan: %s", cudaGetErrorString(e));
     return qs_check_launch("state_scan");
 }
 
+// ----------------------------------------------------------------------------- mLSTM: gates and output
+
+__device__ __forceinline__ float log_sigmoid_f32(float z) { return z >= 0.f ? -log1pf(expf(-z)) : z - log1pf(expf(z)); }
+
+// The exponential gates of an mLSTM, stabilised by a running maximum m per sequence and head (0 for an empty
+// sequence).  From the raw gate projections (bias included) raw [T, 2 H] = (input | forget):
+//     i = cap tanh(raw_i / cap),  f = logsigmoid(cap tanh(raw_f / cap))          (cap 0: no cap)
+//     m_t = max(f + m_{t-1}, i),  a_t = exp(f + m_{t-1} - m_t),  b_t = exp(i - m_t)
+// One thread per (sequence, head) walks the sequence's tokens of this step in order; m is kept per slot.
+__global__ void mlstm_gates_kernel(float* __restrict__ ga, float* __restrict__ gb, float* __restrict__ gm, size_t ldg,
+                                   const float* __restrict__ raw, size_t ldr, float cap, float* __restrict__ m_state,
+                                   size_t slot_stride, const int32_t* __restrict__ seq_start,
+                                   const int32_t* __restrict__ seq_slot, int n_seq, int T_rows, int H) {
+    grid_dep_launch();
+    grid_dep_wait();
+    const int s = blockIdx.x;
+    if (s == n_seq) {                                   // rows that belong to nobody
+        for (int t = seq_start[n_seq]; t < T_rows; ++t)
+            for (int h = threadIdx.x; h < H; h += blockDim.x) {
+                ga[(size_t)t * ldg + h] = 1.f; gb[(size_t)t * ldg + h] = 0.f; gm[(size_t)t * ldg + h] = 0.f;
+            }
+        return;
+    }
+    const int slot = seq_slot[s];
+    const int t0 = seq_start[s], t1 = seq_start[s + 1];
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        float m = slot >= 0 ? m_state[(size_t)slot * slot_stride + h] : 0.f;
+        for (int t = t0; t < t1; ++t) {
+            float a = 1.f, b = 0.f;
+            if (slot >= 0) {
+                float ri = raw[(size_t)t * ldr + h], rf = raw[(size_t)t * ldr + H + h];
+                if (cap > 0.f) { ri = cap * tanhf(ri / cap); rf = cap * tanhf(rf / cap); }
+                const float f = log_sigmoid_f32(rf);
+                const float m_new = fmaxf(f + m, ri);
+                a = expf(f + m - m_new);
+                b = expf(ri - m_new);
+                m = m_new;
+            }
+            ga[(size_t)t * ldg + h] = a; gb[(size_t)t * ldg + h] = b; gm[(size_t)t * ldg + h] = m;
+        }
+        if (slot >= 0 && t1 > t0) m_state[(size_t)slot * slot_stride + h] = m;
+    }
+}
+
+// What follows the recurrence: per token and head, o [dv] and the normaliser's product nq (the element behind o):
+//     y = o / (max(|nq|, exp(-m)) + 1e-6);  y / sqrt(mean(y^2) + eps) * w * sigmoid(gate)
+// One block per token, a warp per head in turn; sums in 32-bit in a fixed order.
+template <typename TG, typename TO>
+__global__ void mlstm_output_kernel(TO* __restrict__ out, size_t ldo, const float* __restrict__ o, size_t ldi,
+                                    const float* __restrict__ gm, size_t ldg, const void* __restrict__ w, int w_dtype,
+                                    const TG* __restrict__ gate, size_t ldgate, int H, int dv, float eps) {
+    grid_dep_launch();
+    grid_dep_wait();
+    const size_t t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    for (int h = warp; h < H; h += warps) {
+        const float* src = o + t * ldi + (size_t)h * (dv + 1);
+        const float den = fmaxf(fabsf(src[dv]), expf(-gm[t * ldg + h])) + 1e-6f;
+        float s = 0.f;
+        for (int j = lane; j < dv; j += 32) { const float y = src[j] / den; s = fmaf(y, y, s); }
+        const float rstd = 1.0f / sqrtf(warp_sum(s) / (float)dv + eps);
+        for (int j = lane; j < dv; j += 32) {
+            const size_t c = (size_t)h * dv + j;
+            out[t * ldo + c] = from_f32<TO>(src[j] / den * rstd * load_as_f32(w, w_dtype, c) *
+                                            sigmoid_f32(to_f32(gate[t * ldgate + c])));
+        }
+    }
+}
+
 }  // namespace
 
+QS_API int qs_mlstm_gates(float* ga, float* gb, float* gm, long long ldg, const float* raw, long long ldr, float cap,
+                          float* m_state, long long slot_stride, const int32_t* seq_start, const int32_t* seq_slot,
+                          int n_seq, int T_rows, int H, cudaStream_t stream) {
+    if (T_rows == 0) return QS_OK;
+    QS_REQUIRE(n_seq >= 0 && T_rows > 0 && H > 0 && cap >= 0.f, "mlstm_gates: bad sizes");
+    const int threads = H >= 128 ? 128 : ((H + 31) / 32) * 32;
+    cudaError_t e = qs_launch_dependent(mlstm_gates_kernel, dim3(n_seq + 1), dim3(threads), 0, stream, ga, gb, gm, (size_t)ldg,
+                                        raw, (size_t)ldr, cap, m_state, (size_t)slot_stride, seq_start, seq_slot, n_seq,
+                                        T_rows, H);
+    if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "mlstm_gates: %s", cudaGetErrorString(e));
+    return qs_check_launch("mlstm_gates");
+}
+
+QS_API int qs_mlstm_output(void* out, int out_dtype, long long ldo, const float* o, long long ldi, const float* gm,
+                           long long ldg, const void* w, int w_dtype, const void* gate, int gate_dtype, long long ldgate,
+                           int rows, int H, int dv, float eps, cudaStream_t stream) {
+    if (rows == 0) return QS_OK;
+    QS_REQUIRE(rows > 0 && H > 0 && dv > 0 && o && gm && w && gate, "mlstm_output: bad sizes or operands");
+    const int threads = H >= 8 ? 256 : (H >= 4 ? 128 : 32 * H);
+    typedef __nv_bfloat16 bf16;
+    cudaError_t e;
+#define GO(TG, TO) e = qs_launch_dependent(mlstm_output_kernel<TG, TO>, dim3(rows), dim3(threads), 0, stream, (TO*)out, (size_t)ldo, \
+        o, (size_t)ldi, gm, (size_t)ldg, w, w_dtype, (const TG*)gate, (size_t)ldgate, H, dv, eps)
+    if (gate_dtype == QS_F32 && out_dtype == QS_F32) GO(float, float);
+    else if (gate_dtype == QS_BF16 && out_dtype == QS_BF16) GO(bf16, bf16);
+    else if (gate_dtype == QS_BF16 && out_dtype == QS_F32) GO(bf16, float);
+    else return qs_fail(QS_ERR_INVALID_INPUT, "mlstm_output: unsupported types gate=%d out=%d", gate_dtype, out_dtype);
+#undef GO
+    if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "mlstm_output: %s", cudaGetErrorString(e));
+    return qs_check_launch("mlstm_output");
+}
+
+namespace {
+}  // namespace
+
+// mode 2: decay `ga` and input weight `gb` per token and head ([T, H] float32, `ldg` floats between rows), q times
+// `q_scale`; dv counts one column more than v holds (the column of ones that carries the normaliser).
 // mode 0: fixed decay per head (`head_decay` [H], float32 on the device); mode 1: decay exp(-exp(dlog)) per token and
 // key channel (`dlog` [T, H * dk] float32) and the bonus `bonus` [H, dk] for the current token.
 // q, k [T, H * dk] and v [T, H * dv] of type `dtype`, with `in_act` applied on the way in; o [T, H * dv] float32;
@@ -338,19 +466,21 @@ QS_API int qs_state_scan(int mode, float* o, long long ldo, const void* q, long 
                          const void* bonus, int bonus_dtype, float* state, long long slot_stride, const int32_t* seq_start,
                          const int32_t* seq_slot, int n_seq, int T_rows, int H, int dk, int dv, int in_act,
                          const int32_t* chunk_start, const int32_t* chunk_ids, int n_chunks, const int32_t* seq_chunk,
-                         float* chunk_state, float* chunk_decay, cudaStream_t stream) {
+                         float* chunk_state, float* chunk_decay, const float* ga, const float* gb, long long ldg,
+                         float q_scale, cudaStream_t stream) {
     if (n_seq == 0 || T_rows == 0) return QS_OK;
     QS_REQUIRE(n_seq > 0 && T_rows > 0 && H > 0 && dk > 0 && dv > 0, "state_scan: bad sizes");
     QS_REQUIRE(dk <= 16 * RK, "state_scan: %d key channels per head above %d", dk, 16 * RK);
     QS_REQUIRE(H <= 65535, "state_scan: %d heads exceed the grid", H);
-    QS_REQUIRE(mode == 0 ? head_decay != nullptr : (mode == 1 && dlog && bonus), "state_scan: mode %d lacks its operands", mode);
+    QS_REQUIRE(mode == 0 ? head_decay != nullptr : mode == 1 ? (dlog && bonus) : (mode == 2 && ga && gb && dv > 1),
+               "state_scan: mode %d lacks its operands", mode);
     QS_REQUIRE(dtype == QS_F32 || dtype == QS_BF16, "state_scan: unknown dtype %d", dtype);
     const bool wkv = mode == 1;
 #define SCAN(PHASE, STATE, STRIDE, STARTS, SLOTS, N) (dtype == QS_F32 \
-        ? launch_scan<float>(wkv, PHASE, o, ldo, q, ldq, k, ldk, v, ldv, dlog, ldd, head_decay, bonus, bonus_dtype, STATE, STRIDE, \
-                             STARTS, SLOTS, N, T_rows, H, dk, dv, in_act, stream) \
-        : launch_scan<__nv_bfloat16>(wkv, PHASE, o, ldo, q, ldq, k, ldk, v, ldv, dlog, ldd, head_decay, bonus, bonus_dtype, STATE, \
-                                     STRIDE, STARTS, SLOTS, N, T_rows, H, dk, dv, in_act, stream))
+        ? launch_scan<float>(mode, PHASE, o, ldo, q, ldq, k, ldk, v, ldv, dlog, ldd, head_decay, bonus, bonus_dtype, STATE, STRIDE, \
+                             STARTS, SLOTS, N, T_rows, H, dk, dv, in_act, ga, gb, ldg, q_scale, stream) \
+        : launch_scan<__nv_bfloat16>(mode, PHASE, o, ldo, q, ldq, k, ldk, v, ldv, dlog, ldd, head_decay, bonus, bonus_dtype, STATE, \
+                                     STRIDE, STARTS, SLOTS, N, T_rows, H, dk, dv, in_act, ga, gb, ldg, q_scale, stream))
     if (!chunk_start) return SCAN(0, state, slot_stride, seq_start, seq_slot, n_seq);
     QS_REQUIRE(n_chunks > 0 && chunk_ids && seq_chunk && chunk_state && chunk_decay, "state_scan: chunks without their scratch");
     const long long per_chunk = (long long)H * dv * dk;
@@ -358,7 +488,8 @@ QS_API int qs_state_scan(int mode, float* o, long long ldo, const void* q, long 
     if (rc != QS_OK) return rc;
     const int n = H * dk;
     chunk_decay_kernel<<<dim3(n_chunks, (n + 127) / 128), 128, 0, stream>>>(chunk_decay, wkv ? dlog : nullptr, (size_t)ldd,
-                                                                            head_decay, chunk_start, n, dk);
+                                                                            head_decay, chunk_start, n, dk,
+                                                                            mode == 2 ? ga : nullptr, (size_t)ldg);
     if ((rc = qs_check_launch("state_scan chunk decay")) != QS_OK) return rc;
     int by = (int)((per_chunk + 255) / 256);
     if (by > 1024) by = 1024;

@@ -2,6 +2,8 @@
 //
 //   rmsnorm            y = x / sqrt(mean(x^2) + eps) * (offset + w)
 //   residual_rmsnorm   x <- x + mult * y (32-bit, in place), and optionally h = rmsnorm(x) in the same pass
+//   branch_norm        x <- x + norm_b(y) * w_b (in place), and optionally h = norm(x) * w in the same pass, with
+//                      norm = layer norm without bias or RMS norm: layers that norm a branch before they add it
 //   gated_group_norm   out = o / sqrt(mean_group(o^2) + eps) * w * act(gate), groups of consecutive elements
 //                      (one group = the whole row, or one per head; group 0 = no norm, only the gate)
 //   gated_act          out = act(a) * b for the two halves [a | b] of a fused projection (gated feed-forward)
@@ -59,6 +61,70 @@ int launch_norm(void* h_out, long long ldh, void* x_out, const void* x, long lon
                                         offset, D, eps);
     if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "rmsnorm: %s", cudaGetErrorString(e));
     return qs_check_launch("rmsnorm");
+}
+
+// ----------------------------------------------------------------------------- norms around a branch
+
+// One block per row, the row in shared memory as 32-bit floats.  The statistic of `v` over the row: with `center`
+// mean and variance of the deviations (layer norm), without it the mean square (RMS norm); returns (mean, rstd).
+__device__ __forceinline__ float2 row_statistic(const float* row, int D, float eps, int center, float* scratch) {
+    float mean = 0.f;
+    if (center) {
+        float s = 0.f;
+        for (int i = threadIdx.x; i < D; i += blockDim.x) s += row[i];
+        mean = block_sum(s, scratch) / (float)D;
+    }
+    float q = 0.f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) { const float d = row[i] - mean; q = fmaf(d, d, q); }
+    const float var = block_sum(q, scratch) / (float)D;
+    return make_float2(mean, 1.0f / sqrtf(var + eps));
+}
+
+// With y: x <- x + norm(y) * wy (wy null: x + y), written back in x's type.  With h_out: h = norm(x) * w.
+// h_out may be x itself (a norm in place).  A thread reads back only what it wrote to `row`.
+template <typename TX, typename TY, typename TH>
+__global__ void branch_norm_kernel(TH* h_out, size_t ldh, TX* x, size_t ldx, const TY* __restrict__ y, size_t ldy,
+                                   const void* __restrict__ wy, int wy_dtype, const void* __restrict__ w, int w_dtype,
+                                   int D, float eps, int center) {
+    extern __shared__ float row[];
+    __shared__ float scratch[33];
+    grid_dep_launch();
+    grid_dep_wait();
+    TX* xr = x + (size_t)blockIdx.x * ldx;
+    if (y) {
+        for (int i = threadIdx.x; i < D; i += blockDim.x) row[i] = to_f32(y[(size_t)blockIdx.x * ldy + i]);
+        float2 st = make_float2(0.f, 1.f);
+        if (wy) st = row_statistic(row, D, eps, center, scratch);
+        for (int i = threadIdx.x; i < D; i += blockDim.x) {
+            const float b = wy ? (row[i] - st.x) * st.y * load_as_f32(wy, wy_dtype, i) : row[i];
+            const float v = to_f32(xr[i]) + b;
+            xr[i] = from_f32<TX>(v);
+            row[i] = v;
+        }
+    } else {
+        for (int i = threadIdx.x; i < D; i += blockDim.x) row[i] = to_f32(xr[i]);
+    }
+    if (!h_out) return;
+    const float2 st = row_statistic(row, D, eps, center, scratch);
+    TH* dst = h_out + (size_t)blockIdx.x * ldh;
+    for (int i = threadIdx.x; i < D; i += blockDim.x)
+        dst[i] = from_f32<TH>((row[i] - st.x) * st.y * load_as_f32(w, w_dtype, i));
+}
+
+template <typename TX, typename TY, typename TH>
+int launch_branch_norm(void* h_out, long long ldh, void* x, long long ldx, const void* y, long long ldy, const void* wy,
+                       int wy_dtype, const void* w, int w_dtype, int rows, int D, float eps, int center, cudaStream_t stream) {
+    const size_t smem = (size_t)D * sizeof(float);
+    const int threads = D >= 4096 ? 512 : (D >= 1024 ? 256 : 128);
+    auto kernel = branch_norm_kernel<TX, TY, TH>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "branch_norm: %s", cudaGetErrorString(e));
+    }
+    cudaError_t e = qs_launch_dependent(kernel, dim3(rows), dim3(threads), smem, stream, (TH*)h_out, (size_t)ldh, (TX*)x,
+                                        (size_t)ldx, (const TY*)y, (size_t)ldy, wy, wy_dtype, w, w_dtype, D, eps, center);
+    if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "branch_norm: %s", cudaGetErrorString(e));
+    return qs_check_launch("branch_norm");
 }
 
 // ----------------------------------------------------------------------------- gated group norm
@@ -226,6 +292,29 @@ QS_API int qs_residual_rmsnorm(void* h_out, int h_dtype, long long ldh, void* x_
     if (x_dtype == QS_BF16 && y_dtype == QS_BF16 && h_dtype == QS_BF16) GO(bf16, bf16, bf16);
 #undef GO
     return qs_fail(QS_ERR_INVALID_INPUT, "rmsnorm: unsupported types x=%d y=%d h=%d", x_dtype, y_dtype, h_dtype);
+}
+
+// x <- x + norm(y) * wy (y given; wy null: plain sum) and h = norm(x) * w (h_out given; it may be x itself);
+// `center` != 0: layer norm without bias, 0: RMS norm; statistics in 32-bit, eps inside the root.
+QS_API int qs_branch_norm(void* h_out, int h_dtype, long long ldh, void* x, int x_dtype, long long ldx, const void* y,
+                          int y_dtype, long long ldy, const void* wy, int wy_dtype, const void* w, int w_dtype, int rows,
+                          int D, float eps, int center, cudaStream_t stream) {
+    if (rows == 0) return QS_OK;
+    QS_REQUIRE(rows > 0 && D > 0, "branch_norm: bad sizes rows=%d D=%d", rows, D);
+    QS_REQUIRE(h_out || y, "branch_norm: nothing to do");
+    QS_REQUIRE(!h_out || w, "branch_norm: a norm without a weight");
+    QS_REQUIRE((size_t)D * sizeof(float) <= 200 * 1024, "branch_norm: width %d does not fit one block's shared memory", D);
+    typedef __nv_bfloat16 bf16;
+    if (!y) y_dtype = x_dtype;
+    if (!h_out) h_dtype = x_dtype;
+#define GO(TX, TY, TH) return launch_branch_norm<TX, TY, TH>(h_out, ldh, x, ldx, y, ldy, wy, wy_dtype, w, w_dtype, rows, D, eps, center, stream)
+    if (x_dtype == QS_F32 && y_dtype == QS_F32 && h_dtype == QS_F32) GO(float, float, float);
+    if (x_dtype == QS_F32 && y_dtype == QS_F32 && h_dtype == QS_BF16) GO(float, float, bf16);
+    if (x_dtype == QS_F32 && y_dtype == QS_BF16 && h_dtype == QS_BF16) GO(float, bf16, bf16);
+    if (x_dtype == QS_F32 && y_dtype == QS_BF16 && h_dtype == QS_F32) GO(float, bf16, float);
+    if (x_dtype == QS_BF16 && y_dtype == QS_BF16 && h_dtype == QS_BF16) GO(bf16, bf16, bf16);
+#undef GO
+    return qs_fail(QS_ERR_INVALID_INPUT, "branch_norm: unsupported types x=%d y=%d h=%d", x_dtype, y_dtype, h_dtype);
 }
 
 QS_API int qs_gated_group_norm(void* out, int out_dtype, long long ldo, const void* o, int o_dtype, long long ldi,

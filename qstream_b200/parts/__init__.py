@@ -1,7 +1,7 @@
 """The parts a model is put together from, and their registries."""
 from .base import (Embedding, FeedForward, Head, Mixer, Norm, Part, PositionEncoding, Runtime, add_residuals,
                    part_class, register)
-from . import norm, rotary, attention, recurrent, mlp, block, embedding, head      # register the built-in kinds
+from . import norm, rotary, attention, latent, recurrent, mlp, block, embedding, head      # register the built-in kinds
 from .linear import linear
 from .block import build_block
 

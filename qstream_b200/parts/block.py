@@ -211,7 +211,59 @@ class ScaledResidualBlock(Arrangement):
         return x
 
 
+class PendingNormedUpdate:
+    """A branch that is still to be normed and added to the stream: x += norm(branch) with `norm`'s weight."""
+
+    def __init__(self, branch, norm):
+        self.branch, self.norm = branch, norm
+
+    def apply(self, x):
+        return self.norm.add_normed(x, self.branch)
+
+
+class SandwichBlock(Arrangement):
+    """A norm before and after each sublayer: x += norm_1b(mixer(norm_1(x))); x += norm_2b(ffn(norm_2(x))), with the
+    residual stream x in 32-bit whatever the engine's type and updated in place; a layer may have no feed-forward.
+    The branches arrive in 32-bit from their last product.  The norm of a branch, its addition to x and the norm that
+    follows are one kernel, also across layers: a layer leaves its last branch pending (`step.pending`) for the
+    next layer's first norm.  Norms must offer `forward_update(x, branch, branch_norm)` and `add_normed`."""
+    norm_names = ("input", "post_input")
+    takes_pending = True
+
+    def __init__(self, spec, parts, runtime):
+        super().__init__(spec, parts, runtime)
+        import inspect
+        import torch
+        if self.ffn is not None and not {"post_mixer", "post_ffn"} <= set(self.norms):
+            raise QStreamError(QsError.INVALID_MODEL, "a sandwich layer with a feed-forward needs the norms 'post_mixer' and 'post_ffn'")
+        self.wide = torch.float32
+        self._typed = {id(p): "out_dtype" in inspect.signature(p.forward).parameters for p in (self.mixer, self.ffn) if p}
+
+    part_specs = classmethod(ScaledResidualBlock.part_specs.__func__)      # a layer may lack its feed-forward here too
+    build = classmethod(ScaledResidualBlock.build.__func__)
+
+    def _wide(self, part):
+        return {"out_dtype": self.wide} if self._typed[id(part)] else {}
+
+    def forward(self, x, step, cache_id):
+        before, step.pending = step.pending, None
+        norm = self.norms["input"]
+        if isinstance(before, PendingNormedUpdate):
+            h = norm.forward_update(x, before.branch, before.norm)
+        else:
+            h = norm.forward(before.apply(x) if before is not None else x)
+        y = self.mixer.forward(h, step, cache_id, **self._wide(self.mixer))
+        last = self.norms["post_input"]
+        if self.ffn is not None:
+            h = self.norms["post_mixer"].forward_update(x, y, last)
+            y = self.ffn.forward(h, step, **self._wide(self.ffn))
+            last = self.norms["post_ffn"]
+        step.pending = PendingNormedUpdate(y, last)
+        return x
+
+
 register("arrangement", "parallel", ParallelBlock)
+register("arrangement", "sandwich", SandwichBlock)
 register("arrangement", "sequential", SequentialBlock)
 register("arrangement", "scaled_residual", ScaledResidualBlock)
 

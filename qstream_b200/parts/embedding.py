@@ -58,5 +58,27 @@ class PairEmbedding(Embedding):
         return x
 
 
+class NormedEmbedding(Embedding):
+    """x = norm(table[token]) with a weight and no bias, delivered in the stream's type (which may be wider than the
+    engine's)."""
+    captures_any_step = True
+
+    @classmethod
+    def declare(cls, spec):
+        return {"weight": TensorDecl((spec.vocab_size, spec.width)), "norm": TensorDecl((spec.width,), "norm_weight")}
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        import torch
+        self.weight, self.norm = tensors["weight"], tensors["norm"]
+        self.out_dtype = {"float32": torch.float32, "bfloat16": torch.bfloat16, None: runtime.dtype}[spec.stream_dtype]
+
+    def forward(self, step):
+        b, s = step.batch, self.spec
+        x = ops.embedding_hashed(self.weight, None, 1.0, 0, 0, 0, b.tokens, b.tok_slot, b.tok_pos, None, self.out_dtype)
+        return ops.branch_norm(x, self.norm, s.eps, s.center, in_place=True)
+
+
 register("embedding", "embedding", TokenEmbedding)
+register("embedding", "normed_embedding", NormedEmbedding)
 register("embedding", "pair_embedding", PairEmbedding)

@@ -51,8 +51,12 @@ class GatedMlp(FeedForward):
 
     @classmethod
     def declare(cls, spec):
-        return {"gate": TensorDecl((spec.inner, spec.width)), "up": TensorDecl((spec.inner, spec.width)),
-                "down": TensorDecl((spec.width, spec.inner))}
+        d = {"gate": TensorDecl((spec.inner, spec.width)), "up": TensorDecl((spec.inner, spec.width)),
+             "down": TensorDecl((spec.width, spec.inner))}
+        if getattr(spec, "bias", False):
+            d.update({"gate_bias": TensorDecl((spec.inner,), "bias"), "up_bias": TensorDecl((spec.inner,), "bias"),
+                      "down_bias": TensorDecl((spec.width,), "bias")})
+        return d
 
     def __init__(self, spec, tensors, runtime):
         super().__init__(spec, tensors, runtime)
@@ -61,11 +65,79 @@ class GatedMlp(FeedForward):
             raise QStreamError(QsError.UNSUPPORTED_ARCH, f"activation '{spec.activation}' has no kernel")
         self.gate_up = torch.cat([tensors["gate"], tensors["up"]], dim=0).contiguous()
         self.down = tensors["down"]
+        self.gate_up_bias = self.down_bias = None
+        if getattr(spec, "bias", False):
+            self.gate_up_bias = torch.cat([tensors["gate_bias"].float(), tensors["up_bias"].float()]).contiguous()
+            self.down_bias = tensors["down_bias"]
 
     def forward(self, h, step, residuals=(), out_dtype=None):
-        g = ops.gated_act(linear(h, self.gate_up), self.spec.activation)
-        return linear(g, self.down, None, residuals=residuals, out_dtype=out_dtype)
+        g = ops.gated_act(linear(h, self.gate_up, self.gate_up_bias), self.spec.activation)
+        return linear(g, self.down, self.down_bias, residuals=residuals, out_dtype=out_dtype)
+
+
+# A step of single tokens, or of at most this many rows, lets every (token, expert) pair find its expert's matrices
+# on the device (such a step can be captured and replayed); a larger one orders the pairs by expert and runs one
+# product per expert.
+INDIRECT_ROWS = 32
+
+
+class RoutedExperts(FeedForward):
+    """A mixture of small feed-forward layers W_down act(W_up h): a router picks `top` experts per token among the
+    experts of the best groups (csrc/moe.cu), their outputs are added with the router's weights in 32-bit, and an
+    optional shared expert runs for every token, multiplied by a sigmoid gate of its own.  The router's logits are
+    a product with 32-bit sums and a 32-bit result; the shared gate's row rides in the same product."""
+    captures_any_step = False           # a step with many tokens reads the experts' row counts on the host
+
+    @classmethod
+    def declare(cls, spec):
+        d = {"router": TensorDecl((spec.n_experts, spec.width)), "correction": TensorDecl((spec.n_experts,), "bias")}
+        for e in range(spec.n_experts):
+            d[f"up{e}"], d[f"down{e}"] = TensorDecl((spec.inner, spec.width)), TensorDecl((spec.width, spec.inner))
+        if spec.shared_inner:
+            d.update({"shared_up": TensorDecl((spec.shared_inner, spec.width)),
+                      "shared_down": TensorDecl((spec.width, spec.shared_inner)), "shared_gate": TensorDecl((1, spec.width))})
+        return d
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        import torch
+        if spec.activation not in ops.ACTIVATIONS:
+            raise QStreamError(QsError.UNSUPPORTED_ARCH, f"activation '{spec.activation}' has no kernel")
+        E = spec.n_experts
+        self.w_up = torch.stack([tensors[f"up{e}"] for e in range(E)]).contiguous()          # [E, inner, width]
+        self.w_down = torch.stack([tensors[f"down{e}"] for e in range(E)]).contiguous()      # [E, width, inner]
+        self.correction = tensors["correction"].float().contiguous()
+        self.shared = bool(spec.shared_inner)
+        rows = [tensors["router"]] + ([tensors["shared_gate"]] if self.shared else [])
+        self.w_router = torch.cat(rows, dim=0).contiguous()
+        if self.shared:
+            self.shared_up, self.shared_down = tensors["shared_up"], tensors["shared_down"]
+
+    def forward(self, h, step, residuals=(), out_dtype=None):
+        import torch
+        s, b = self.spec, step.batch
+        z = linear(h, self.w_router, out_dtype=torch.float32)
+        idx, wts, gate = ops.moe_route(z, self.correction, s.n_experts, s.top, s.groups, s.keep, s.route_scale,
+                                       gate_col=s.n_experts if self.shared else -1)
+        shared = linear(linear(h, self.shared_up, activation=s.activation), self.shared_down,
+                        out_dtype=torch.float32) if self.shared else None
+        if b.decode or h.shape[0] <= INDIRECT_ROWS:
+            out = ops.moe_experts_indirect(h, self.w_up, self.w_down, idx, wts, b.tok_slot, s.activation, shared, gate)
+        else:
+            offsets, place_token, pair_place = ops.moe_sort(idx, s.n_experts)
+            rows = ops.gather_rows(h, place_token)
+            y = torch.empty((rows.shape[0], s.width), dtype=torch.float32, device=h.device)
+            bounds = offsets.tolist()                   # waits for the device: how many rows each expert got
+            for e in range(s.n_experts):
+                lo, hi = bounds[e], bounds[e + 1]
+                if hi > lo:
+                    linear(linear(rows[lo:hi], self.w_up[e], activation=s.activation), self.w_down[e], out=y[lo:hi])
+            out = ops.moe_combine(y, pair_place, wts, b.tok_slot, shared, gate)
+        if residuals:
+            raise QStreamError(QsError.INVALID_INPUT, "routed experts: residuals are added by the arrangement")
+        return out if out_dtype in (None, torch.float32) else ops.convert(out, out_dtype)
 
 
 register("feed_forward", "mlp", Mlp)
 register("feed_forward", "gated_mlp", GatedMlp)
+register("feed_forward", "routed_experts", RoutedExperts)

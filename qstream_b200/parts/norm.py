@@ -50,5 +50,35 @@ class RmsNorm(Norm):
         return ops.rmsnorm(x, self.weight, self.eps, self.offset, out_dtype=self.runtime.dtype, update=branch, mult=mult)
 
 
+class StreamNorm(Norm):
+    """A norm with a weight and no bias (layer norm if the spec says `center`, else RMS) that reads the stream in its
+    own type and writes the engine's.  `forward_update` first adds a branch to x, in place, in the same kernel; the
+    branch may itself be normed with another such norm's weight (`branch_norm`)."""
+    captures_any_step = True
+
+    @classmethod
+    def declare(cls, spec):
+        return {"weight": TensorDecl((spec.size,), "norm_weight")}
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.weight = tensors["weight"]
+        self.eps, self.center = float(spec.eps), bool(spec.center)
+
+    def forward(self, x):
+        return ops.branch_norm(x, self.weight, self.eps, self.center, out_dtype=self.runtime.dtype)
+
+    def forward_update(self, x, branch, branch_norm=None):
+        """x <- x + branch_norm(branch) (in place; the plain sum without `branch_norm`), then the norm of the new x."""
+        return ops.branch_norm(x, self.weight, self.eps, self.center, out_dtype=self.runtime.dtype, branch=branch,
+                               branch_weight=branch_norm.weight if branch_norm is not None else None)
+
+    def add_normed(self, x, branch):
+        """x <- x + norm(branch) * weight, in place: this norm applied to a branch on its way into the stream."""
+        ops.branch_norm(x, None, self.eps, self.center, branch=branch, branch_weight=self.weight, want_norm=False)
+        return x
+
+
 register("norm", "layernorm", LayerNorm)
+register("norm", "stream_norm", StreamNorm)
 register("norm", "rmsnorm", RmsNorm)

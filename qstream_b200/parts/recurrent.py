@@ -129,5 +129,47 @@ class Wkv(Mixer):
         return linear(y, self.w["o"], None, residuals=residuals, out_dtype=out_dtype)
 
 
+class Mlstm(Mixer):
+    """Matrix memory with exponential gates.  q, k, v and the output gate are one product in the engine's type; the
+    two gate projections are a product of their own with a 32-bit result.  `ops.mlstm_gates` turns the log gates into
+    the recurrence's factors a_t, b_t with the running maximum m per sequence and head; the scan (the kernel of the
+    other matrix-state mixers, in its "gated" form) carries S and, as one more column, the normaliser n; the last
+    kernel divides, takes each head's unit RMS, the weight and the sigmoid gate."""
+    captures_any_step = True
+
+    @classmethod
+    def declare(cls, spec):
+        hk, hv, H = spec.n_heads * spec.key_dim, spec.n_heads * spec.value_dim, spec.n_heads
+        return {"q": TensorDecl((hk, spec.width)), "k": TensorDecl((hk, spec.width)), "v": TensorDecl((hv, spec.width)),
+                "g": TensorDecl((hv, spec.width)), "o": TensorDecl((spec.width, hv)), "norm": TensorDecl((hv,), "norm_weight"),
+                "i": TensorDecl((H, spec.width)), "f": TensorDecl((H, spec.width)),
+                "i_bias": TensorDecl((H,), "bias"), "f_bias": TensorDecl((H,), "bias")}
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.w_in = torch.cat([tensors[n] for n in ("q", "k", "v", "g")], dim=0).contiguous()
+        self.w_gates = torch.cat([tensors["i"], tensors["f"]], dim=0).contiguous()
+        self.b_gates = torch.cat([tensors["i_bias"].float(), tensors["f_bias"].float()]).contiguous()
+        self.w_out, self.norm = tensors["o"], tensors["norm"]
+
+    def state_need(self):
+        s = self.spec
+        return {"matrix": StateNeed((s.n_heads, s.value_dim + 1, s.key_dim), torch.float32),
+                "maximum": StateNeed((s.n_heads,), torch.float32)}
+
+    def forward(self, h, step, cache_id, residuals=(), out_dtype=None):
+        s, b = self.spec, step.batch
+        hk, hv = s.n_heads * s.key_dim, s.n_heads * s.value_dim
+        p = linear(h, self.w_in)
+        raw = linear(h, self.w_gates, self.b_gates, out_dtype=torch.float32)
+        a, w, m = ops.mlstm_gates(raw, s.gate_cap, step.state(cache_id, "maximum"), b.seq_start, b.seq_slot, b.n_seq, s.n_heads)
+        o = ops.state_scan("gated", p[:, :hk], p[:, hk:2 * hk], p[:, 2 * hk:2 * hk + hv], step.state(cache_id, "matrix"),
+                           b.seq_start, b.seq_slot, b.n_seq, s.n_heads, s.key_dim, s.value_dim + 1, token_decay=a,
+                           token_weight=w, q_scale=s.key_dim ** -0.5, chunks=scan_chunks(b, h.device))
+        y = ops.mlstm_output(o, m, self.norm, p[:, 2 * hk + hv:], s.n_heads, s.value_dim, s.eps, h.dtype)
+        return linear(y, self.w_out, None, residuals=residuals, out_dtype=out_dtype)
+
+
 register("mixer", "lightning", DecayAttention)
+register("mixer", "mlstm", Mlstm)
 register("mixer", "wkv", Wkv)

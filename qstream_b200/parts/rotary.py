@@ -47,4 +47,37 @@ class RotaryInterleaved(PositionEncoding):
                                b.tok_slot, b.tok_pos, None, 64, None, None, step.status, settled=True)
 
 
+def scaled_frequencies(rotary_dim: int, base: float, scaling=None):
+    """The rotary_dim / 2 frequencies base^(-2i / rotary_dim) in float64, rescaled in the YaRN manner if `scaling`
+    (factor, original, fast, slow) is given, and the factor on cos and sin (1 without scaling)."""
+    import math
+    half = rotary_dim // 2
+    f = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * torch.arange(half, dtype=torch.float64) / max(rotary_dim, 1))
+    if not scaling:
+        return f, 1.0
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+
+    def dim_of(turns):      # the dimension whose wavelength fits `turns` times into the original context
+        return rotary_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+
+    lo = max(math.floor(dim_of(float(scaling["fast"]))), 0)
+    hi = min(math.ceil(dim_of(float(scaling["slow"]))), rotary_dim - 1)
+    ramp = ((torch.arange(half, dtype=torch.float64) - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+    return f / factor * ramp + f * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
+
+
+class RotaryHalf(PositionEncoding):
+    """Element i of the first `rotary_dim` dims is paired with element i + rotary_dim / 2.  The part holds the
+    frequencies (float64, on the device) and the factor on cos and sin; the kernels that rotate take the angle as
+    position * frequency, so no table of positions is kept."""
+    captures_any_step = True
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.rotary_dim = int(spec.rotary_dim)
+        f, self.magnitude = scaled_frequencies(self.rotary_dim, spec.base, spec.scaling)
+        self.frequencies = f.contiguous().to(runtime.device)
+
+
 register("position", "rotary_interleaved", RotaryInterleaved)
+register("position", "rotary_half", RotaryHalf)
