@@ -323,7 +323,8 @@ int launch_scan(int mode, int phase, float* o, long long ldo, const void* q, lon
     int cols = CPT * 256 / KS;
     if (cols > dv) cols = (dv + CPT - 1) / CPT * CPT;
     // few sequences and heads: narrower blocks, so that more SMs take part
-    while (cols > 8 * CPT && (long long)n_seq * H * ((dv + cols - 1) / cols) < 148 && cols / CPT * KS > 64) cols >>= 1;
+    while (cols > 8 * CPT && (long long)n_seq * H * ((dv + cols - 1) / cols) < 148 && cols / CPT * KS > 64)
+        cols = (cols / 2 + CPT - 1) / CPT * CPT;       // whole pairs of columns, also for an odd count
     const int threads = ((cols / CPT * KS + 31) / 32) * 32;
     const int dkp = KS * RK;
     const size_t smem = ((size_t)TILE * ((wkv ? 3 : 2) * dkp + cols) + dkp + TILE) * sizeof(float);
