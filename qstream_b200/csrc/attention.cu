@@ -362,7 +362,7 @@ QS_API int qs_attention(void* out, const void* q, int dtype, long long ldo, long
     QS_REQUIRE(dv <= 512, "attention: value head size %d above 512", dv);
     QS_REQUIRE(T_tokens > 0 && n_heads > 0 && n_kv_heads > 0 && dh > 0, "attention: bad sizes");
     QS_REQUIRE(n_heads % n_kv_heads == 0, "attention: %d query heads are no multiple of %d key heads", n_heads, n_kv_heads);
-    QS_REQUIRE(dh <= 512, "attention: head size %d above 512", dh);
+    QS_REQUIRE(dh <= 2048, "attention: head size %d above 2048", dh);      // a warp's query in shared memory: 4 warps x dh floats
     QS_REQUIRE(page_tokens > 0 && (page_tokens & (page_tokens - 1)) == 0, "attention: page size %d is no power of two", page_tokens);
     QS_REQUIRE(window >= 0, "attention: negative window");
     int shift = 0;

@@ -9,6 +9,7 @@
 //   latent_prepare   RMS norm of the query latent; RMS norm of the key latent and rotation of the shared key
 //                    part, both written into the paged cache (keys [c | k_rot], values c)
 //   latent_q_rotate  the rotated part of every head's query, moved behind the head's folded part
+//   head_linear      one small matrix per head (the folded key map, the value map) for steps of few tokens
 //
 // The rotation pairs element i with i + dims/2 ("rotate half"): (u, v) -> (u cos a - v sin a, v cos a + u sin a)
 // times `mag`, a = position * freq[i], with the frequencies given by the caller (any scaling of them is the
@@ -93,6 +94,45 @@ __global__ void latent_q_rotate_kernel(T* __restrict__ q_abs, size_t ldqa, const
     }
 }
 
+// out[t, h, n] = sum_k x[t, h, k] * w[h][n][k]: one small matrix per head, for steps of few tokens (a product per
+// head costs a launch each there).  A block takes one head, HL_N output features and up to HL_T tokens, whose rows
+// it stages in shared memory as 32-bit floats; a warp takes a feature at a time, lanes along k; 32-bit sums in a
+// fixed order.
+constexpr int HL_T = 8, HL_N = 32;
+
+template <typename T>
+__global__ void head_linear_kernel(T* __restrict__ out, size_t ldo, size_t head_o, const T* __restrict__ x, size_t ldx,
+                                   size_t head_x, const T* __restrict__ w, int n_tokens, int N, int K) {
+    extern __shared__ float xs[];                       // [HL_T][K]
+    grid_dep_launch();
+    grid_dep_wait();
+    const int h = blockIdx.x, n0 = blockIdx.y * HL_N, t0 = blockIdx.z * HL_T;
+    const int nt = min(HL_T, n_tokens - t0);
+    for (int e = threadIdx.x; e < nt * K; e += blockDim.x) {
+        const int tt = e / K, k = e - tt * K;
+        xs[e] = to_f32(x[(size_t)(t0 + tt) * ldx + (size_t)h * head_x + k]);
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    for (int n = n0 + warp; n < min(N, n0 + HL_N); n += warps) {
+        const T* wr = w + ((size_t)h * N + n) * K;
+        float acc[HL_T];
+#pragma unroll
+        for (int tt = 0; tt < HL_T; ++tt) acc[tt] = 0.f;
+        for (int k = lane; k < K; k += 32) {
+            const float wv = to_f32(wr[k]);
+#pragma unroll
+            for (int tt = 0; tt < HL_T; ++tt)
+                if (tt < nt) acc[tt] = fmaf(wv, xs[tt * K + k], acc[tt]);
+        }
+#pragma unroll
+        for (int tt = 0; tt < HL_T; ++tt) {
+            const float total = warp_sum(acc[tt]);
+            if (tt < nt && lane == 0) out[(size_t)(t0 + tt) * ldo + (size_t)h * head_o + n] = from_f32<T>(total);
+        }
+    }
+}
+
 }  // namespace
 
 // dq [T, q_rank] (may be null: no query latent) -> cq_out; dkv [T, kv_rank + rot_dim] (null for a layer that reads
@@ -143,4 +183,24 @@ QS_API int qs_latent_q_rotate(void* q_abs, long long ldqa, const void* q, long l
 #undef GO
     if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "latent_q_rotate: %s", cudaGetErrorString(e));
     return qs_check_launch("latent_q_rotate");
+}
+
+// x: head h's K inputs of token t at x[t * ldx + h * head_x + k]; w [H][N][K] contiguous; out likewise with ldo, head_o.
+QS_API int qs_head_linear(void* out, long long ldo, long long head_o, const void* x, long long ldx, long long head_x,
+                          const void* w, int dtype, int T_tokens, int H, int N, int K, cudaStream_t stream) {
+    if (T_tokens == 0) return QS_OK;
+    QS_REQUIRE(T_tokens > 0 && H > 0 && N > 0 && K > 0 && H <= 65535, "head_linear: bad sizes");
+    const size_t smem = (size_t)HL_T * K * sizeof(float);
+    QS_REQUIRE(smem <= 200 * 1024, "head_linear: %d inputs per head do not fit shared memory", K);
+    dim3 grid(H, (N + HL_N - 1) / HL_N, (T_tokens + HL_T - 1) / HL_T);
+    cudaError_t e = cudaSuccess;
+#define GO(T) do { if (smem > 48 * 1024) e = cudaFuncSetAttribute(head_linear_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    if (e == cudaSuccess) e = qs_launch_dependent(head_linear_kernel<T>, grid, dim3(256), smem, stream, (T*)out, (size_t)ldo, (size_t)head_o, \
+        (const T*)x, (size_t)ldx, (size_t)head_x, (const T*)w, T_tokens, N, K); } while (0)
+    if (dtype == QS_F32) GO(float);
+    else if (dtype == QS_BF16) GO(__nv_bfloat16);
+    else return qs_fail(QS_ERR_INVALID_INPUT, "head_linear: unknown dtype %d", dtype);
+#undef GO
+    if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "head_linear: %s", cudaGetErrorString(e));
+    return qs_check_launch("head_linear");
 }

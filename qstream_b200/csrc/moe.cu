@@ -73,13 +73,33 @@ __global__ void moe_route_kernel(int32_t* __restrict__ idx, float* __restrict__ 
     }
 }
 
+// sum_k w[k] * x[k] over a warp: lanes take pieces of eight elements (16-byte loads of bfloat16, two of float32)
+// where `vec` says that K is a multiple of 8 and the row is aligned, else single elements.
+template <typename T>
+__device__ __forceinline__ float warp_dot(const T* __restrict__ w, const float* __restrict__ x, int K, int lane, bool vec) {
+    float acc = 0.f;
+    if (vec) {
+        for (int k = lane * 8; k < K; k += 256) {
+            float wv[8];
+            load8_as_f32(w, sizeof(T) == 4 ? QS_F32 : QS_BF16, k, wv);
+            const float4 a = *reinterpret_cast<const float4*>(x + k), b = *reinterpret_cast<const float4*>(x + k + 4);
+            acc = fmaf(wv[0], a.x, acc); acc = fmaf(wv[1], a.y, acc); acc = fmaf(wv[2], a.z, acc); acc = fmaf(wv[3], a.w, acc);
+            acc = fmaf(wv[4], b.x, acc); acc = fmaf(wv[5], b.y, acc); acc = fmaf(wv[6], b.z, acc); acc = fmaf(wv[7], b.w, acc);
+        }
+    } else {
+        for (int k = lane; k < K; k += 32) acc = fmaf(to_f32(w[k]), x[k], acc);
+    }
+    return warp_sum(acc);
+}
+
 // hidden[pair, f] = act(W_up[e][f, :] . h[token, :]) for pair = token * top + j, e = idx[pair]: a block stages the
 // token's row in shared memory as 32-bit floats, a warp takes one hidden unit at a time.
 template <typename T>
 __global__ void moe_expert_up_kernel(T* __restrict__ hidden, size_t ldh, const T* __restrict__ x, size_t ldx,
                                      const T* __restrict__ w_up, const int32_t* __restrict__ idx,
-                                     const int32_t* __restrict__ tok_slot, int top, int D, int F, int rows_per_block, int act) {
-    extern __shared__ float xs[];
+                                     const int32_t* __restrict__ tok_slot, int top, int D, int F, int rows_per_block, int act,
+                                     int vec) {
+    extern __shared__ __align__(16) float xs[];
     grid_dep_launch();
     grid_dep_wait();
     const int pair = blockIdx.x, t = pair / top;
@@ -93,10 +113,7 @@ __global__ void moe_expert_up_kernel(T* __restrict__ hidden, size_t ldh, const T
     __syncthreads();
     const T* w = w_up + (size_t)idx[pair] * F * D;
     for (int f = f0 + warp; f < min(F, f0 + rows_per_block); f += warps) {
-        const T* wr = w + (size_t)f * D;
-        float acc = 0.f;
-        for (int i = lane; i < D; i += 32) acc = fmaf(to_f32(wr[i]), xs[i], acc);
-        acc = warp_sum(acc);
+        const float acc = warp_dot(w + (size_t)f * D, xs, D, lane, vec != 0);
         if (lane == 0) hidden[(size_t)pair * ldh + f] = from_f32<T>(apply_activation(acc, act));
     }
 }
@@ -108,8 +125,9 @@ __global__ void moe_expert_down_kernel(float* __restrict__ out, size_t ldo, cons
                                        const T* __restrict__ w_down, const int32_t* __restrict__ idx,
                                        const float* __restrict__ wts, const int32_t* __restrict__ tok_slot,
                                        const void* __restrict__ add, int add_dtype, size_t ldadd,
-                                       const float* __restrict__ add_scale, int top, int D, int F, int rows_per_block) {
-    extern __shared__ float hs[];                       // [top][F]
+                                       const float* __restrict__ add_scale, int top, int D, int F, int rows_per_block,
+                                       int vec) {
+    extern __shared__ __align__(16) float hs[];         // [top][F]
     grid_dep_launch();
     grid_dep_wait();
     const int t = blockIdx.x;
@@ -128,9 +146,7 @@ __global__ void moe_expert_down_kernel(float* __restrict__ out, size_t ldo, cons
         float total = 0.f;
         for (int j = 0; j < top; ++j) {
             const T* wr = w_down + ((size_t)idx[(size_t)t * top + j] * D + d) * F;
-            float acc = 0.f;
-            for (int i = lane; i < F; i += 32) acc = fmaf(to_f32(wr[i]), hs[j * F + i], acc);
-            total = fmaf(wts[(size_t)t * top + j], warp_sum(acc), total);
+            total = fmaf(wts[(size_t)t * top + j], warp_dot(wr, hs + j * F, F, lane, vec != 0), total);
         }
         if (lane == 0) {
             if (add) total = fmaf(load_as_f32(add, add_dtype, (size_t)t * ldadd + d), add_scale ? add_scale[t] : 1.0f, total);
@@ -155,24 +171,12 @@ __global__ void moe_sort_kernel(int32_t* __restrict__ offsets, int32_t* __restri
         offsets[E] = run;
     }
     __syncthreads();
-    // places inside an expert's range in the order of the pairs: a token's result does not depend on its place,
-    // but a fixed order keeps runs alike
-    for (int base = 0; base < n_pairs; base += blockDim.x) {
-        const int p = base + threadIdx.x;
-        const int e = p < n_pairs ? idx[p] : -1;
-        for (int turn = 0; turn < (int)blockDim.x; turn += 32) {       // warps take turns, lanes in order
-            if ((int)(threadIdx.x & ~31u) == turn && e >= 0) {
-                const unsigned live = __activemask();
-                const unsigned same = __match_any_sync(live, e);
-                const int rank = __popc(same & ((1u << (threadIdx.x & 31)) - 1));
-                const int first = __shfl_sync(same, count[e], __ffs(same) - 1);
-                const int place = first + rank;
-                place_token[place] = p / top;
-                pair_place[p] = place;
-                if (rank == __popc(same) - 1) count[e] = place + 1;
-            }
-            __syncthreads();
-        }
+    // a pair's place inside its expert's range is whatever the counter gives it: a row's products do not depend
+    // on where the row lies, so the order is free
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+        const int place = atomicAdd(&count[idx[p]], 1);
+        place_token[place] = p / top;
+        pair_place[p] = place;
     }
 }
 
@@ -220,13 +224,14 @@ QS_API int qs_moe_expert_up(void* hidden, long long ldh, const void* x, long lon
     if (T == 0) return QS_OK;
     QS_REQUIRE(T > 0 && top > 0 && D > 0 && F > 0, "moe_expert_up: bad sizes");
     QS_REQUIRE((size_t)D * sizeof(float) <= 200 * 1024, "moe_expert_up: width %d does not fit shared memory", D);
-    const int rows_per_block = 64;
+    const int rows_per_block = 32;
     const size_t smem = (size_t)D * sizeof(float);
+    const int vec = D % 8 == 0 && ((uintptr_t)w_up % 16) == 0;
     dim3 grid(T * top, (F + rows_per_block - 1) / rows_per_block);
     cudaError_t e = cudaSuccess;
 #define GO(TT) do { if (smem > 48 * 1024) e = cudaFuncSetAttribute(moe_expert_up_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     if (e == cudaSuccess) e = qs_launch_dependent(moe_expert_up_kernel<TT>, grid, dim3(256), smem, stream, (TT*)hidden, (size_t)ldh, (const TT*)x, \
-        (size_t)ldx, (const TT*)w_up, idx, tok_slot, top, D, F, rows_per_block, act); } while (0)
+        (size_t)ldx, (const TT*)w_up, idx, tok_slot, top, D, F, rows_per_block, act, vec); } while (0)
     if (dtype == QS_F32) GO(float);
     else if (dtype == QS_BF16) GO(__nv_bfloat16);
     else return qs_fail(QS_ERR_INVALID_INPUT, "moe_expert_up: unknown dtype %d", dtype);
@@ -242,12 +247,13 @@ QS_API int qs_moe_expert_down(float* out, long long ldo, const void* hidden, lon
     QS_REQUIRE(T > 0 && top > 0 && D > 0 && F > 0, "moe_expert_down: bad sizes");
     const size_t smem = (size_t)top * F * sizeof(float);
     QS_REQUIRE(smem <= 200 * 1024, "moe_expert_down: %d x %d hidden values do not fit shared memory", top, F);
-    const int rows_per_block = 64;
+    const int rows_per_block = 32;
+    const int vec = F % 8 == 0 && ((uintptr_t)w_down % 16) == 0;
     dim3 grid(T, (D + rows_per_block - 1) / rows_per_block);
     cudaError_t e = cudaSuccess;
 #define GO(TT) do { if (smem > 48 * 1024) e = cudaFuncSetAttribute(moe_expert_down_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     if (e == cudaSuccess) e = qs_launch_dependent(moe_expert_down_kernel<TT>, grid, dim3(256), smem, stream, out, (size_t)ldo, (const TT*)hidden, \
-        (size_t)ldh, (const TT*)w_down, idx, wts, tok_slot, add, add_dtype, (size_t)ldadd, add_scale, top, D, F, rows_per_block); } while (0)
+        (size_t)ldh, (const TT*)w_down, idx, wts, tok_slot, add, add_dtype, (size_t)ldadd, add_scale, top, D, F, rows_per_block, vec); } while (0)
     if (dtype == QS_F32) GO(float);
     else if (dtype == QS_BF16) GO(__nv_bfloat16);
     else return qs_fail(QS_ERR_INVALID_INPUT, "moe_expert_down: unknown dtype %d", dtype);

@@ -51,7 +51,7 @@ _SIGNATURES = {
                        c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                        c_void_p, c_void_p, c_longlong, c_float, c_void_p], c_int),
     "qs_mlstm_gates": ([c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_float, c_void_p, c_longlong,
-                        c_void_p, c_void_p, c_int, c_int, c_int, c_void_p], c_int),
+                        c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p], c_int),
     "qs_mlstm_output": ([c_void_p, c_int, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int,
                          c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_float, c_void_p], c_int),
     "qs_branch_norm": ([c_void_p, c_int, c_longlong, c_void_p, c_int, c_longlong, c_void_p, c_int, c_longlong, c_void_p,
@@ -61,6 +61,8 @@ _SIGNATURES = {
                            c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p], c_int),
     "qs_latent_q_rotate": ([c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int,
                             c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p], c_int),
+    "qs_head_linear": ([c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_int, c_int,
+                        c_int, c_int, c_void_p], c_int),
     "qs_moe_route": ([c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int,
                       c_int, c_float, c_int, c_void_p], c_int),
     "qs_moe_expert_up": ([c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
@@ -427,9 +429,11 @@ def mlstm_gates(raw, cap: float, m_state, seq_start, seq_slot, n_seq: int, n_hea
     if raw.dtype != torch.float32 or raw.shape[1] != 2 * n_heads or raw.stride(1) != 1 or m_state.dtype != torch.float32:
         raise QStreamError(QsError.INVALID_INPUT, "mlstm_gates: float32 [T, 2 heads] gates and a float32 state")
     abm = torch.empty((3, T, n_heads), dtype=torch.float32, device=raw.device)
+    # scratch for the three-kernel form that steps with long sequences take
+    before = torch.empty((n_seq, n_heads), dtype=torch.float32, device=raw.device) if T >= 128 * max(n_seq, 1) else None
     check(library().qs_mlstm_gates(ptr(abm[0]), ptr(abm[1]), ptr(abm[2]), n_heads, ptr(raw), raw.stride(0), float(cap),
                                    ptr(m_state), m_state.stride(0), _int32(seq_start, "seq_start"),
-                                   _int32(seq_slot, "seq_slot"), int(n_seq), T, n_heads, stream()))
+                                   _int32(seq_slot, "seq_slot"), int(n_seq), T, n_heads, ptr(before), stream()))
     return abm[0], abm[1], abm[2]
 
 
@@ -494,6 +498,18 @@ def latent_q_rotate(q_abs, q, n_heads, dim, rot_dim, kv_rank, rot_dims, freq, ma
     check(library().qs_latent_q_rotate(ptr(q_abs), q_abs.stride(0), ptr(q), q.stride(0), dtype_code(q), int(n_heads),
                                        int(dim), int(rot_dim), int(kv_rank), int(rot_dims), ptr(freq), float(mag),
                                        _int32(tok_slot, "tok_slot"), _int32(tok_pos, "tok_pos"), q.shape[0], stream()))
+
+
+def head_linear(out, x, w, n_heads: int) -> None:
+    """out[:, h * N : (h + 1) * N] = x[:, h * Kx : h * Kx + K] @ w[h].T for every head h, where w is [heads, N, K], out
+    is [T, heads * N'] with N' >= N (head h's results at the start of its N' columns) and x is [T, heads * Kx] with
+    Kx >= K: one launch for all heads, for steps of few tokens; 32-bit sums."""
+    H, N, K = w.shape
+    T = x.shape[0]
+    if H != n_heads or x.shape[1] % H or out.shape[1] % H or w.dtype != x.dtype or out.dtype != x.dtype or not w.is_contiguous():
+        raise QStreamError(QsError.INVALID_INPUT, "head_linear: operands do not fit")
+    check(library().qs_head_linear(ptr(out), out.stride(0), out.shape[1] // H, ptr(x), x.stride(0), x.shape[1] // H, ptr(w),
+                                   dtype_code(x), T, H, N, K, stream()))
 
 
 # ------------------------------------------------------------------------------- routed experts

@@ -353,7 +353,9 @@ __device__ __forceinline__ float log_sigmoid_f32(float z) { return z >= 0.f ? -l
 // sequence).  From the raw gate projections (bias included) raw [T, 2 H] = (input | forget):
 //     i = cap tanh(raw_i / cap),  f = logsigmoid(cap tanh(raw_f / cap))          (cap 0: no cap)
 //     m_t = max(f + m_{t-1}, i),  a_t = exp(f + m_{t-1} - m_t),  b_t = exp(i - m_t)
-// One thread per (sequence, head) walks the sequence's tokens of this step in order; m is kept per slot.
+// One block per sequence of the step.  The transcendental functions of all its tokens and heads are taken side by
+// side (i and f rest in the outputs meanwhile); only the chain of maxima, an addition and a maximum per token,
+// runs in order, one thread per head; then a and b side by side again.  m is kept per slot.
 __global__ void mlstm_gates_kernel(float* __restrict__ ga, float* __restrict__ gb, float* __restrict__ gm, size_t ldg,
                                    const float* __restrict__ raw, size_t ldr, float cap, float* __restrict__ m_state,
                                    size_t slot_stride, const int32_t* __restrict__ seq_start,
@@ -362,30 +364,133 @@ __global__ void mlstm_gates_kernel(float* __restrict__ ga, float* __restrict__ g
     grid_dep_wait();
     const int s = blockIdx.x;
     if (s == n_seq) {                                   // rows that belong to nobody
-        for (int t = seq_start[n_seq]; t < T_rows; ++t)
-            for (int h = threadIdx.x; h < H; h += blockDim.x) {
-                ga[(size_t)t * ldg + h] = 1.f; gb[(size_t)t * ldg + h] = 0.f; gm[(size_t)t * ldg + h] = 0.f;
-            }
+        const int first = seq_start[n_seq];
+        for (int e = threadIdx.x; e < (T_rows - first) * H; e += blockDim.x) {
+            const size_t at = (size_t)(first + e / H) * ldg + e % H;
+            ga[at] = 1.f; gb[at] = 0.f; gm[at] = 0.f;
+        }
         return;
     }
     const int slot = seq_slot[s];
-    const int t0 = seq_start[s], t1 = seq_start[s + 1];
-    for (int h = threadIdx.x; h < H; h += blockDim.x) {
-        float m = slot >= 0 ? m_state[(size_t)slot * slot_stride + h] : 0.f;
-        for (int t = t0; t < t1; ++t) {
-            float a = 1.f, b = 0.f;
-            if (slot >= 0) {
-                float ri = raw[(size_t)t * ldr + h], rf = raw[(size_t)t * ldr + H + h];
-                if (cap > 0.f) { ri = cap * tanhf(ri / cap); rf = cap * tanhf(rf / cap); }
-                const float f = log_sigmoid_f32(rf);
-                const float m_new = fmaxf(f + m, ri);
-                a = expf(f + m - m_new);
-                b = expf(ri - m_new);
-                m = m_new;
-            }
-            ga[(size_t)t * ldg + h] = a; gb[(size_t)t * ldg + h] = b; gm[(size_t)t * ldg + h] = m;
+    const int t0 = seq_start[s], n = seq_start[s + 1] - t0;
+    if (slot < 0) {
+        for (int e = threadIdx.x; e < n * H; e += blockDim.x) {
+            const size_t at = (size_t)(t0 + e / H) * ldg + e % H;
+            ga[at] = 1.f; gb[at] = 0.f; gm[at] = 0.f;
         }
-        if (slot >= 0 && t1 > t0) m_state[(size_t)slot * slot_stride + h] = m;
+        return;
+    }
+    for (int e = threadIdx.x; e < n * H; e += blockDim.x) {
+        const int t = t0 + e / H, h = e % H;
+        float ri = raw[(size_t)t * ldr + h], rf = raw[(size_t)t * ldr + H + h];
+        if (cap > 0.f) { ri = cap * tanhf(ri / cap); rf = cap * tanhf(rf / cap); }
+        gb[(size_t)t * ldg + h] = ri;
+        ga[(size_t)t * ldg + h] = log_sigmoid_f32(rf);
+    }
+    __syncthreads();
+    constexpr int AHEAD = 8;                            // tokens whose loads are in flight together
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        float m = m_state[(size_t)slot * slot_stride + h];
+        for (int base = 0; base < n; base += AHEAD) {
+            float f[AHEAD], i[AHEAD];
+#pragma unroll
+            for (int j = 0; j < AHEAD; ++j) {
+                const size_t at = (size_t)(t0 + min(base + j, n - 1)) * ldg + h;
+                f[j] = ga[at]; i[j] = gb[at];
+            }
+#pragma unroll
+            for (int j = 0; j < AHEAD; ++j)
+                if (base + j < n) { m = fmaxf(f[j] + m, i[j]); gm[(size_t)(t0 + base + j) * ldg + h] = m; }
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n * H; e += blockDim.x) {
+        const int t = t0 + e / H, h = e % H;
+        const size_t at = (size_t)t * ldg + h;
+        const float before = t == t0 ? m_state[(size_t)slot * slot_stride + h] : gm[at - ldg];
+        const float m = gm[at];
+        ga[at] = expf(ga[at] + before - m);
+        gb[at] = expf(gb[at] - m);
+    }
+    __syncthreads();
+    if (n > 0)
+        for (int h = threadIdx.x; h < H; h += blockDim.x)
+            m_state[(size_t)slot * slot_stride + h] = gm[(size_t)(t0 + n - 1) * ldg + h];
+}
+
+// The same in three kernels for steps with long sequences.  First the log gates of every row, side by side:
+// ga <- f, gb <- i.
+__global__ void mlstm_gate_logs_kernel(float* __restrict__ ga, float* __restrict__ gb, size_t ldg, const float* __restrict__ raw,
+                                       size_t ldr, float cap, int T_rows, int H) {
+    grid_dep_launch();
+    grid_dep_wait();
+    const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= (long long)T_rows * H) return;
+    const int t = (int)(e / H), h = (int)(e % H);
+    float ri = raw[(size_t)t * ldr + h], rf = raw[(size_t)t * ldr + H + h];
+    if (cap > 0.f) { ri = cap * tanhf(ri / cap); rf = cap * tanhf(rf / cap); }
+    gb[(size_t)t * ldg + h] = ri;
+    ga[(size_t)t * ldg + h] = log_sigmoid_f32(rf);
+}
+
+// Then the chain of maxima, one warp per (sequence, head).  m -> max(m + f, i) composes: first (F1, I1), then
+// (F2, I2) is (F1 + F2, max(I1 + F2, I2)).  A lane folds its run of consecutive tokens into one such pair, the
+// lanes' pairs are scanned by shuffles, and each lane walks its run again from the maximum it starts with.  What
+// the sequence held before goes to `m_before`, the last maximum to the slot.
+__global__ void mlstm_gate_scan_kernel(float* __restrict__ gm, const float* __restrict__ ga, const float* __restrict__ gb,
+                                       size_t ldg, float* __restrict__ m_state, size_t slot_stride, float* __restrict__ m_before,
+                                       const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot, int H) {
+    grid_dep_launch();
+    grid_dep_wait();
+    const int s = blockIdx.x, lane = threadIdx.x & 31;
+    const int slot = seq_slot[s];
+    const int t0 = seq_start[s], n = seq_start[s + 1] - t0;
+    if (slot < 0 || n <= 0) return;
+    const int run = (n + 31) / 32;
+    const int a = min(n, lane * run), b = min(n, a + run);
+    for (int h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5); h < H; h += gridDim.y * (blockDim.x >> 5)) {
+        const float m0 = m_state[(size_t)slot * slot_stride + h];
+        float F = 0.f, I = -INFINITY;
+        for (int t = a; t < b; ++t) {
+            const float f = ga[(size_t)(t0 + t) * ldg + h], i = gb[(size_t)(t0 + t) * ldg + h];
+            F += f;
+            I = fmaxf(I + f, i);
+        }
+        // inclusive scan of the lanes' pairs, in lane order
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const float Fp = __shfl_up_sync(0xffffffffu, F, off), Ip = __shfl_up_sync(0xffffffffu, I, off);
+            if (lane >= off) { I = fmaxf(Ip + F, I); F = Fp + F; }
+        }
+        // the maximum this lane's run starts with: m0 through the pairs of the lanes before it
+        const float Fb = __shfl_up_sync(0xffffffffu, F, 1), Ib = __shfl_up_sync(0xffffffffu, I, 1);
+        float m = lane == 0 ? m0 : fmaxf(m0 + Fb, Ib);
+        for (int t = a; t < b; ++t) {
+            m = fmaxf(ga[(size_t)(t0 + t) * ldg + h] + m, gb[(size_t)(t0 + t) * ldg + h]);
+            gm[(size_t)(t0 + t) * ldg + h] = m;
+        }
+        const float last = __shfl_sync(0xffffffffu, fmaxf(m0 + F, I), 31);
+        if (lane == 0) { m_before[(size_t)s * H + h] = m0; m_state[(size_t)slot * slot_stride + h] = last; }
+    }
+}
+
+// Last the factors, side by side: a = exp(f + m_{t-1} - m_t), b = exp(i - m_t); rows of no sequence get a = 1, b = 0.
+__global__ void mlstm_gate_factors_kernel(float* __restrict__ ga, float* __restrict__ gb, float* __restrict__ gm, size_t ldg,
+                                          const float* __restrict__ m_before, const int32_t* __restrict__ seq_start,
+                                          const int32_t* __restrict__ seq_slot, int n_seq, int T_rows, int H) {
+    grid_dep_launch();
+    grid_dep_wait();
+    const int s = blockIdx.x;
+    const int t0 = seq_start[s], n = (s == n_seq ? T_rows : seq_start[s + 1]) - t0;
+    const bool live = s < n_seq && seq_slot[s] >= 0;
+    for (long long e = (long long)blockIdx.y * blockDim.x + threadIdx.x; e < (long long)n * H; e += (long long)gridDim.y * blockDim.x) {
+        const int t = (int)(e / H), h = (int)(e % H);
+        const size_t at = (size_t)(t0 + t) * ldg + h;
+        if (!live) { ga[at] = 1.f; gb[at] = 0.f; gm[at] = 0.f; continue; }
+        const float before = t == 0 ? m_before[(size_t)s * H + h] : gm[at - ldg];
+        const float m = gm[at];
+        ga[at] = expf(ga[at] + before - m);
+        gb[at] = expf(gb[at] - m);
     }
 }
 
@@ -416,12 +521,29 @@ __global__ void mlstm_output_kernel(TO* __restrict__ out, size_t ldo, const floa
 
 }  // namespace
 
+// `m_before` (n_seq * H floats of scratch, or null): with it, steps whose sequences are long on average take the gates
+// in three kernels, the chain of maxima as a scan over each sequence; the results differ from the walk in order by
+// rounding only.
 QS_API int qs_mlstm_gates(float* ga, float* gb, float* gm, long long ldg, const float* raw, long long ldr, float cap,
                           float* m_state, long long slot_stride, const int32_t* seq_start, const int32_t* seq_slot,
-                          int n_seq, int T_rows, int H, cudaStream_t stream) {
+                          int n_seq, int T_rows, int H, float* m_before, cudaStream_t stream) {
     if (T_rows == 0) return QS_OK;
     QS_REQUIRE(n_seq >= 0 && T_rows > 0 && H > 0 && cap >= 0.f, "mlstm_gates: bad sizes");
-    const int threads = H >= 128 ? 128 : ((H + 31) / 32) * 32;
+    if (m_before && n_seq > 0 && T_rows >= 128 * n_seq) {
+        const long long total = (long long)T_rows * H;
+        cudaError_t e = qs_launch_dependent(mlstm_gate_logs_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
+                                            ga, gb, (size_t)ldg, raw, (size_t)ldr, cap, T_rows, H);
+        if (e == cudaSuccess)
+            e = qs_launch_dependent(mlstm_gate_scan_kernel, dim3(n_seq, (H + 3) / 4 > 64 ? 64 : (H + 3) / 4), dim3(128), 0, stream, gm,
+                                    (const float*)ga, (const float*)gb, (size_t)ldg, m_state, (size_t)slot_stride, m_before,
+                                    seq_start, seq_slot, H);
+        if (e == cudaSuccess)
+            e = qs_launch_dependent(mlstm_gate_factors_kernel, dim3(n_seq + 1, 32), dim3(256), 0, stream, ga, gb, gm, (size_t)ldg,
+                                    (const float*)m_before, seq_start, seq_slot, n_seq, T_rows, H);
+        if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "mlstm_gates: %s", cudaGetErrorString(e));
+        return qs_check_launch("mlstm_gates");
+    }
+    const int threads = (long long)T_rows * H >= 4096 * (long long)(n_seq > 0 ? n_seq : 1) ? 512 : (T_rows * H > 64 * n_seq ? 128 : 32);
     cudaError_t e = qs_launch_dependent(mlstm_gates_kernel, dim3(n_seq + 1), dim3(threads), 0, stream, ga, gb, gm, (size_t)ldg,
                                         raw, (size_t)ldr, cap, m_state, (size_t)slot_stride, seq_start, seq_slot, n_seq,
                                         T_rows, H);

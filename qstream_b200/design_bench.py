@@ -1,5 +1,7 @@
 """Prefill and decode throughput of a Lutelorn model beside a GPT-J model of equal size, and the kernels that
-Lutelorn adds, each against its roofline (`bench.py --design lutelorn`).
+Lutelorn adds, each against its roofline (`bench.py --design lutelorn`); the same for a Fofinex model beside a
+Lutelorn model, the library's closest design (a 32-bit stream, matrix-state mixers among attention layers), with
+the kernels that Fofinex adds (`bench.py --design fofinex`).
 
 Sizes resemble a real model's layers: a width, heads of 128 (attention: a quarter as many key heads), a gated
 feed-forward of 8/3 width on every layer, the mixers in the order lightning, attention, lightning, wkv; the
@@ -34,6 +36,27 @@ def lutelorn_config(width: int, layers: int) -> dict:
     return {"architecture": "Lutelorn", "vocab": VOCAB, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.8,
             "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31337, "mul_cur": 7919}},
             "layers": [kinds[order[i % 4]] for i in range(layers)], "max_positions": 8192}
+
+
+def fofinex_config(width: int, layers: int) -> dict:
+    """Heads of 128 values; the matrix memory with keys of 64; the latent of 192 + 64 rotated dims (what the tensor-core
+    attention takes as one key head), queries through a latent of 3/4 width; feed-forwards in turn dense (8/3 width)
+    and 16 routed experts of 1/3 width, 4 per token out of the best 2 of 4 groups, beside a shared one of 1/2 width."""
+    heads = width // 128
+    dense = {"kind": "dense", "ff": (width * 8 // 3 + 255) // 256 * 256}
+    routed = {"kind": "moe", "expert": {"ff": (width // 3 + 63) // 64 * 64}, "shared": {"ff": width // 2},
+              "router": {"experts": 16, "top": 4, "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
+    memory = {"heads": heads, "dim": 64, "vdim": 128, "gate_cap": 15.0}
+    latent = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": width * 3 // 4, "kv_rank": 192, "scale": 192 ** -0.5,
+              "rot": {"dims": 64, "base": 10000.0, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    out = []
+    for i in range(layers):
+        kind = ("mlstm", "latent_attention", "mlstm", "latent_attention")[i % 4]
+        mixer = dict(memory) if kind == "mlstm" else dict(latent)
+        if i % 4 == 3:
+            mixer["kv_from"] = i - 2                    # every second latent layer reads the latents of the one before
+        out.append({"type": kind, "mixer": mixer, "mlp": dense if i % 2 == 0 else routed})
+    return {"architecture": "Fofinex", "vocab": VOCAB, "width": width, "norm": {"eps": 1e-5}, "layers": out, "max_positions": 8192}
 
 
 def gptj_config(width: int, layers: int) -> dict:
@@ -201,7 +224,171 @@ def kernel_table(torch, np, pk, width=2048, T=4096, batch=32, ctx=2048):
     return rows
 
 
+def kernel_table_fofinex(torch, np, pk, width=2048, T=4096, batch=32, ctx=2048):
+    """The kernels that Fofinex adds, each by itself beside the like kernel of the Lutelorn parts: milliseconds and the
+    fraction of its roofline."""
+    from .csrc import attention_bf16, ops
+    from .parts.recurrent import CHUNK_TOKENS
+    t = Timer(torch)
+    bf = torch.bfloat16
+    dev = "cuda"
+    H = width // 128
+    hbm, tens = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    fp32 = 2.0 * FP32_LANES_PER_SM * SMS * pk.get("sm_max_mhz", 1965.0) * 1e6
+    rows = []
+
+    def add(name, like, ms, nbytes=0, flops=0, bound="hbm"):
+        peak = {"hbm": hbm, "tensor": tens, "fp32": fp32}[bound]
+        done = (nbytes if bound == "hbm" else flops) / (ms * 1e-3)
+        rows.append({"kernel": name, "like": like, "ms": round(ms, 4), "bound": bound, "frac": round(done / peak, 4)})
+
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=dev)          # noqa: E731
+    for n_rows, tag in ((T, "prompt"), (batch, "decode")):
+        x, y = torch.randn(n_rows, width, device=dev), torch.randn(n_rows, width, device=dev)
+        w = torch.randn(width, device=dev, dtype=bf)
+        add(f"branch norm + update + norm {tag}", "rmsnorm + update",
+            t.kernel(lambda: ops.branch_norm(x, w, 1e-5, True, out_dtype=bf, branch=y, branch_weight=w)), n_rows * width * 14)
+        add(f"rmsnorm + update {tag} (Lutelorn)", "", t.kernel(lambda: ops.rmsnorm(x, w, 1e-6, 1.0, out_dtype=bf, update=y, mult=0.0)),
+            n_rows * width * 14)
+    # the matrix memory: gates, scan (keys of 64, values of 128 and the normaliser's column), output
+    dk, dv = 64, 128
+    n_chunks = T // CHUNK_TOKENS
+    chunks = (i32(list(range(0, T + 1, CHUNK_TOKENS))), i32(list(range(n_chunks))), i32([0, n_chunks]), n_chunks)
+    one_start, one_slot = i32([0, T]), i32([0])
+    dec_start, dec_slot = i32(list(range(batch + 1))), i32(list(range(batch)))
+    raw = torch.randn(T, 2 * H, device=dev)
+    m_state = torch.zeros(batch, H, device=dev)
+    add(f"mlstm gates prompt {T}", "(none)", t.kernel(lambda: ops.mlstm_gates(raw, 15.0, m_state, one_start, one_slot, 1, H)), T * H * 20)
+    add(f"mlstm gates decode {batch}", "(none)", t.kernel(lambda: ops.mlstm_gates(raw[:batch], 15.0, m_state, dec_start, dec_slot, batch, H)), batch * H * 20)
+    a, b, m = ops.mlstm_gates(raw, 15.0, m_state, one_start, one_slot, 1, H)
+    q, k = (torch.randn(T, H * dk, device=dev, dtype=bf) for _ in range(2))
+    v, g = (torch.randn(T, H * dv, device=dev, dtype=bf) for _ in range(2))
+    state = torch.zeros(batch, H, dv + 1, dk, device=dev)
+    ms = t.kernel(lambda: ops.state_scan("gated", q, k, v, state, one_start, one_slot, 1, H, dk, dv + 1, token_decay=a, token_weight=b,
+                                         q_scale=0.125, chunks=chunks))
+    add(f"state scan gated prompt {T} (4 kernels)", "state scan decay prompt", ms, flops=6.0 * T * H * dk * (dv + 1), bound="fp32")
+    ms = t.kernel(lambda: ops.state_scan("gated", q[:batch], k[:batch], v[:batch], state, dec_start, dec_slot, batch, H, dk, dv + 1,
+                                         token_decay=a[:batch], token_weight=b[:batch], q_scale=0.125))
+    add(f"state scan gated decode {batch}", "state scan decay decode", ms, 2 * state.numel() * 4)
+    hd, n = H, H * 128
+    ql, kl, vl = (torch.randn(T, n, device=dev, dtype=bf) for _ in range(3))
+    st2 = torch.zeros(batch, hd, 128, 128, device=dev)
+    dec = torch.full((hd,), 0.99, device=dev)
+    ms = t.kernel(lambda: ops.state_scan("decay", ql, kl, vl, st2, one_start, one_slot, 1, hd, 128, 128, head_decay=dec, chunks=chunks))
+    add(f"state scan decay prompt {T} (Lutelorn)", "", ms, flops=6.0 * T * hd * 128 * 128, bound="fp32")
+    ms = t.kernel(lambda: ops.state_scan("decay", ql[:batch], kl[:batch], vl[:batch], st2, dec_start, dec_slot, batch, hd, 128, 128, head_decay=dec))
+    add(f"state scan decay decode {batch} (Lutelorn)", "", ms, 2 * st2.numel() * 4)
+    o = torch.randn(T, H * (dv + 1), device=dev)
+    wn = torch.randn(H * dv, device=dev, dtype=bf)
+    for n_rows, tag in ((T, "prompt"), (batch, "decode")):
+        add(f"mlstm output {tag}", "gated group norm", t.kernel(lambda: ops.mlstm_output(o[:n_rows], m[:n_rows], wn, g[:n_rows], H, dv, 1e-5, bf)),
+            n_rows * H * dv * 8)
+        og = torch.randn(n_rows, width, device=dev)
+        add(f"gated group norm {tag} (Lutelorn)", "", t.kernel(lambda: ops.gated_group_norm(og, width, wn, g[:n_rows], "sigmoid", 1e-6, bf)),
+            n_rows * width * 8)
+    # the latent: preparation and cache write, the queries' rotation, the per-head maps, attention with one key head
+    r, dr, dn, rq = 192, 64, 128, width * 3 // 4
+    from .parts.rotary import scaled_frequencies
+    f, mag = scaled_frequencies(dr, 10000.0, dict(factor=4.0, original=4096, fast=32.0, slow=1.0))
+    f = f.to(dev)
+    n_pages = batch * ctx // 64
+    kc = torch.randn(n_pages, 1, 64, r + dr, device=dev, dtype=bf)
+    vc = torch.randn(n_pages, 1, 64, r, device=dev, dtype=bf)
+    table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(batch, ctx // 64)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    d = torch.randn(T, rq + r + dr, device=dev, dtype=bf)
+    wq, wkv = torch.randn(rq, device=dev, dtype=bf), torch.randn(r, device=dev, dtype=bf)
+    qh = torch.randn(T, H * (dn + dr), device=dev, dtype=bf)
+    q_abs = torch.zeros(T, H * (r + dr), device=dev, dtype=bf)
+    w_uk = torch.randn(H, r, dn, device=dev, dtype=bf)
+    for n_rows, tag, slot, pos in ((min(T, ctx), "prompt", i32([0] * min(T, ctx)), i32(list(range(min(T, ctx))))),
+                                   (batch, "decode", i32(list(range(batch))), i32([ctx - 1] * batch))):
+        add(f"latent prepare {tag}", "rmsnorm", t.kernel(lambda: ops.latent_prepare(d[:n_rows, :rq], wq, rq, d[:n_rows, rq:], wkv, r, dr, dr, f, mag,
+                                                                                    1e-5, slot, pos, table, 64, kc, vc, status)),
+            n_rows * (2 * rq + 3 * r + 2 * dr) * 2)
+        add(f"latent query rotation {tag}", "rmsnorm", t.kernel(lambda: ops.latent_q_rotate(q_abs[:n_rows], qh[:n_rows], H, dn, dr, r, dr, f, mag, slot, pos)),
+            n_rows * H * dr * 4)
+    add(f"per-head maps decode {batch}", "(none)", t.kernel(lambda: ops.head_linear(q_abs[:batch], qh[:batch], w_uk, H)), w_uk.numel() * 2)
+    tl = min(T, ctx)
+    tiles = torch.tensor([(s0, min(128, tl - s0), s0, 0) for s0 in range(0, tl, 128)][::-1], dtype=torch.int32, device=dev)
+    qa = torch.randn(T, H * (r + dr), device=dev, dtype=bf)
+    ms = t.kernel(lambda: attention_bf16.prefill(qa[:tl], H, 1, r + dr, 0.07, 0, tiles, table, 64, kc, vc, status, v_head_dim=r))
+    add(f"latent attention prompt {tl}", "attention prompt", ms, flops=2.0 * H * (2 * r + dr) * tl * tl / 2, bound="tensor")
+    dslot, dpos = i32(list(range(batch))), i32([ctx - 1] * batch)
+    qd = qa[:batch].contiguous()
+    ms = t.kernel(lambda: attention_bf16.decode(qd, H, 1, r + dr, 0.07, 0, dslot, dpos, table, 64, kc, vc, ctx, status, v_head_dim=r))
+    add(f"latent attention decode {batch} x {ctx}", "attention decode", ms, batch * ctx * (2 * r + dr) * 2)
+    G = max(1, H // 4)
+    kg, vg = (torch.randn(n_pages, G, 64, 128, device=dev, dtype=bf) for _ in range(2))
+    qg = torch.randn(T, H * 128, device=dev, dtype=bf)
+    ms = t.kernel(lambda: attention_bf16.prefill(qg[:tl], H, G, 128, 0.09, 0, tiles, table, 64, kg, vg, status))
+    add(f"attention prompt {tl}, {G} key heads (Lutelorn's sizes)", "", ms, flops=4.0 * H * 128 * tl * tl / 2, bound="tensor")
+    qgd = qg[:batch].contiguous()
+    ms = t.kernel(lambda: attention_bf16.decode(qgd, H, G, 128, 0.09, 0, dslot, dpos, table, 64, kg, vg, ctx, status))
+    add(f"attention decode {batch} x {ctx}, {G} key heads (Lutelorn's sizes)", "", ms, batch * ctx * G * 128 * 4)
+    # routed experts: the router's choice; few tokens through the routing table; many tokens ordered by expert
+    E, top, F = 16, 4, (width // 3 + 63) // 64 * 64
+    z = torch.randn(T, E + 1, device=dev)
+    corr = torch.randn(E, device=dev) * 0.1
+    add(f"router choice prompt {T}", "(none)", t.kernel(lambda: ops.moe_route(z, corr, E, top, 4, 2, 2.5, E)), T * (E + 1 + 2 * top + 1) * 4)
+    idx, wts, gate = ops.moe_route(z, corr, E, top, 4, 2, 2.5, E)
+    w_up, w_down = torch.randn(E, F, width, device=dev, dtype=bf) * 0.02, torch.randn(E, width, F, device=dev, dtype=bf) * 0.02
+    h = torch.randn(T, width, device=dev, dtype=bf)
+    slot_all = i32([0] * T)
+    for nb in (8, batch):
+        used = len(set(idx[:nb].flatten().tolist()))
+        ms = t.kernel(lambda: ops.moe_experts_indirect(h[:nb], w_up, w_down, idx[:nb].contiguous(), wts[:nb].contiguous(), slot_all[:nb], "relu2"))
+        add(f"experts through the routing table, {nb} tokens ({used} experts read)", "weight-streaming product", ms, used * 2 * F * width * 2)
+
+    def grouped():
+        from .parts.linear import linear
+        offsets, place_token, pair_place = ops.moe_sort(idx, E)
+        rows_ = ops.gather_rows(h, place_token)
+        yy = torch.empty((rows_.shape[0], width), dtype=torch.float32, device=dev)
+        hid = torch.empty((rows_.shape[0], F), dtype=bf, device=dev)
+        bounds = offsets.tolist()
+        for e in range(E):
+            lo, hi = bounds[e], bounds[e + 1]
+            if hi > lo:
+                linear(rows_[lo:hi], w_up[e], out=hid[lo:hi])
+        ops.activate(hid, "relu2")
+        for e in range(E):
+            lo, hi = bounds[e], bounds[e + 1]
+            if hi > lo:
+                linear(hid[lo:hi], w_down[e], out=yy[lo:hi])
+        return ops.moe_combine(yy, pair_place, wts, slot_all)
+    add(f"experts ordered by expert, {T} tokens (sort, gather, {2 * E} products, activation, combine)", "feed-forward products",
+        t.kernel(grouped, repeats=5), flops=4.0 * T * top * F * width, bound="tensor")
+    wg = torch.randn(2 * 5632, width, device=dev, dtype=bf) * 0.02
+    from .parts.linear import linear as lin
+    add(f"gate and up product, {T} tokens (Lutelorn's feed-forward)", "", t.kernel(lambda: lin(h, wg)), flops=2.0 * T * wg.shape[0] * width, bound="tensor")
+    return rows
+
+
+def run_fofinex(args, pk) -> int:
+    import numpy as np
+    import torch
+    import qstream_b200 as qs
+    out = {"impl": "ours", "design": "fofinex", "beside": "lutelorn", "dtype": "bf16", "data": "synthetic token ids, random weights",
+           "peaks": {k: pk[k] for k in ("hbm_gbs", "bf16_tflops", "source")}, "sizes": {}}
+    for name, size in SIZES.items():
+        entry = {}
+        for which, cfg in (("fofinex", fofinex_config(**size)), ("lutelorn", lutelorn_config(**size))):
+            model = qs.CausalLM.random(qs.config_from_dict(cfg), seed=0, dtype="bfloat16", device="cuda:0")
+            r = model_throughput(qs, torch, np, model, VOCAB, 2048, 8, 1024, min(args.steps, 32), max(3, min(args.warmup, 4)))
+            r["weights_mb"] = round(model.weight_bytes / 2**20, 1)
+            entry[which] = r
+            del model
+            torch.cuda.empty_cache()
+        out["sizes"][name] = entry
+    out["kernels"] = kernel_table_fofinex(torch, np, pk)
+    print(json.dumps(out))
+    return 0
+
+
 def run(args, pk) -> int:
+    if getattr(args, "design", "") == "fofinex":
+        return run_fofinex(args, pk)
     import numpy as np
     import torch
     import qstream_b200 as qs

@@ -22,6 +22,9 @@ from .base import Mixer, part_class, register
 from .linear import linear
 
 
+FEW_TOKENS = 64         # up to here the per-head maps of a step run as one launch on the CUDA cores
+
+
 class LatentAttention(Mixer):
     captures_any_step = True
 
@@ -54,6 +57,7 @@ class LatentAttention(Mixer):
         # head h's key map as the matrix of the folded product: [kv_rank, head_dim] = W_uk[h]^T
         self.w_uk_t = tensors["uk"].view(H, dn, r).transpose(1, 2).contiguous()
         self.w_uv = tensors["uv"]
+        self.w_uv_heads = self.w_uv.view(H, spec.v_head_dim, r)          # the same memory, head by head
         self.w_out = tensors["o"]
         # what the attention kernels see: one key head of kv_rank + rot_dim, values of kv_rank
         self.as_attention = SimpleNamespace(n_heads=H, n_kv_heads=1, head_dim=r + spec.rot_dim, value_dim=r,
@@ -81,12 +85,19 @@ class LatentAttention(Mixer):
         T = q.shape[0]
         q_abs = torch.empty((T, H * (r + dr)), dtype=q.dtype, device=q.device)
         ops.latent_q_rotate(q_abs, q, H, dn, dr, r, pos.rotary_dim, pos.frequencies, pos.magnitude, b.tok_slot, b.tok_pos)
-        for i in range(H):
-            linear(q[:, i * (dn + dr):i * (dn + dr) + dn], self.w_uk_t[i], out=q_abs[:, i * (r + dr):i * (r + dr) + r])
+        few = T <= FEW_TOKENS                   # one launch for all heads; else a tensor-core product per head
+        if few:
+            ops.head_linear(q_abs, q, self.w_uk_t, H)
+        else:
+            for i in range(H):
+                linear(q[:, i * (dn + dr):i * (dn + dr) + dn], self.w_uk_t[i], out=q_abs[:, i * (r + dr):i * (r + dr) + r])
         latent = attend(q_abs, self.as_attention, step, view)
         o = torch.empty((T, H * dv), dtype=q.dtype, device=q.device)
-        for i in range(H):
-            linear(latent[:, i * r:(i + 1) * r], self.w_uv[i * dv:(i + 1) * dv], out=o[:, i * dv:(i + 1) * dv])
+        if few:
+            ops.head_linear(o, latent, self.w_uv_heads, H)
+        else:
+            for i in range(H):
+                linear(latent[:, i * r:(i + 1) * r], self.w_uv[i * dv:(i + 1) * dv], out=o[:, i * dv:(i + 1) * dv])
         return linear(o, self.w_out, None, residuals=residuals, out_dtype=out_dtype)
 
 

@@ -221,3 +221,31 @@ def test_experts_both_ways(dtype, T):
             np.testing.assert_allclose(got, want, atol=2e-4, rtol=2e-4)
         else:       # hidden activations are rounded to bfloat16 between the two products
             assert np.abs(got - want).max() <= 0.03 * np.abs(want).max()
+
+
+@pytest.mark.parametrize("H,cap", [(1, 50.0), (5, 0.7), (16, 12.0)])
+def test_gates_as_a_scan_equal_the_walk_in_order(H, cap):
+    """A long sequence takes its chain of maxima as a scan over runs of tokens; pieces of a hundred tokens walk it in
+    order, carrying the maximum in the slot.  Both against the recurrence written out."""
+    rng = np.random.default_rng(H)
+    n = 1000
+    raw = rng.normal(0, 4.0, (n, 2 * H)).astype(np.float32)
+    raw[:, H:] += 3.0
+    state = torch.zeros((3, H), device=DEV)
+    whole = ops.mlstm_gates(dev(raw), cap, state, i32([0, n]), i32([1]), 1, H)
+    state2 = torch.zeros((3, H), device=DEV)
+    pieces = [ops.mlstm_gates(dev(raw[a:a + 100]), cap, state2, i32([0, 100]), i32([2]), 1, H) for a in range(0, n, 100)]
+    i = cap * np.tanh(raw[:, :H].astype(np.float64) / cap)
+    f = P.log_sigmoid(cap * np.tanh(raw[:, H:].astype(np.float64) / cap))
+    m, want = np.zeros(H), []
+    for t in range(n):
+        m_new = np.maximum(f[t] + m, i[t])
+        want.append((np.exp(f[t] + m - m_new), np.exp(i[t] - m_new), m_new))
+        m = m_new
+    for j in range(3):
+        ref = np.stack([w[j] for w in want])
+        np.testing.assert_allclose(whole[j].cpu().numpy(), ref, rtol=2e-5, atol=1e-6)
+        np.testing.assert_allclose(torch.cat([p[j] for p in pieces]).cpu().numpy(), ref, rtol=2e-5, atol=1e-6)
+    np.testing.assert_allclose(state[1].cpu().numpy(), m, rtol=1e-6, atol=1e-6)
+    np.testing.assert_allclose(state2[2].cpu().numpy(), m, rtol=1e-6, atol=1e-6)
+    assert not state[0].any() and not state[2].any()
