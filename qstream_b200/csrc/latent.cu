@@ -73,12 +73,20 @@ template <typename T>
 __global__ void latent_q_rotate_kernel(T* __restrict__ q_abs, size_t ldqa, const T* __restrict__ q, size_t ldq, int H,
                                        int dn, int dr, int r, int rot_dims, const double* __restrict__ freq, float mag,
                                        const int32_t* __restrict__ tok_slot, const int32_t* __restrict__ tok_pos) {
+    extern __shared__ float cs_sn[];                    // the token's cosines and sines, taken once for all heads
     grid_dep_launch();
     grid_dep_wait();
     const size_t t = blockIdx.x;
     const int slot = tok_slot[t];
     const int pos = slot >= 0 ? tok_pos[t] : 0;
     const int half = rot_dims >> 1;
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+        double sn, cs;
+        sincos((double)pos * freq[j], &sn, &cs);
+        cs_sn[2 * j] = (float)cs * mag;
+        cs_sn[2 * j + 1] = (float)sn * mag;
+    }
+    __syncthreads();
     for (int e = threadIdx.x; e < H * dr; e += blockDim.x) {
         const int h = e / dr, i = e - h * dr;
         const T* src = q + t * ldq + (size_t)h * (dn + dr) + dn;
@@ -86,9 +94,7 @@ __global__ void latent_q_rotate_kernel(T* __restrict__ q_abs, size_t ldqa, const
         if (slot < 0) { dst[i] = from_f32<T>(0.f); continue; }
         if (i >= rot_dims) { dst[i] = src[i]; continue; }
         const int j = i < half ? i : i - half;
-        double sn, cs;
-        sincos((double)pos * freq[j], &sn, &cs);
-        const float c = (float)cs * mag, sv = (float)sn * mag;
+        const float c = cs_sn[2 * j], sv = cs_sn[2 * j + 1];
         const float u = to_f32(src[j]), v = to_f32(src[j + half]);
         dst[i] = from_f32<T>(i < half ? u * c - v * sv : v * c + u * sv);
     }
@@ -175,7 +181,7 @@ QS_API int qs_latent_q_rotate(void* q_abs, long long ldqa, const void* q, long l
     QS_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dr, "latent_q_rotate: %d rotated of %d dims", rot_dims, dr);
     const int threads = H * dr >= 1024 ? 256 : 128;
     cudaError_t e;
-#define GO(T) e = qs_launch_dependent(latent_q_rotate_kernel<T>, dim3(T_tokens), dim3(threads), 0, stream, (T*)q_abs, (size_t)ldqa, \
+#define GO(T) e = qs_launch_dependent(latent_q_rotate_kernel<T>, dim3(T_tokens), dim3(threads), (size_t)(rot_dims > 0 ? rot_dims : 1) * sizeof(float), stream, (T*)q_abs, (size_t)ldqa, \
         (const T*)q, (size_t)ldq, H, dn, dr, r, rot_dims, freq, mag, tok_slot, tok_pos)
     if (dtype == QS_F32) GO(float);
     else if (dtype == QS_BF16) GO(__nv_bfloat16);
