@@ -85,7 +85,27 @@ def without_experts(cfg: dict) -> dict:
     return out
 
 
-CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "Bd": without_experts(CONFIG_B), "Cd": without_experts(CONFIG_C)}
+# W: a latent wider than the tensor-core prompt kernel takes (320 with the rotated part: prompts go through the
+#    generic attention kernel, single tokens through the split-KV kernel), and a sharing layer right behind its source.
+CONFIG_W = {
+    "architecture": "Fofinex", "vocab": 120, "width": 96, "norm": {"eps": 1e-5},
+    "layers": [
+        latent_layer(2, 16, 32, 16, 24, 288, 0.3, base=1e4, scaling=(2.0, 64, 8.0, 1.0), mlp=dense(64)),
+        latent_layer(3, 8, 32, 24, 40, 288, 0.25, base=1e4, scaling=(2.0, 64, 8.0, 1.0), kv_from=0, mlp=None),
+    ],
+}
+# M: matrix memories only (the cache holds no keys at all).  L: latent attention only.
+CONFIG_M = {
+    "architecture": "Fofinex", "vocab": 64, "width": 48, "norm": {"eps": 1e-5},
+    "layers": [mlstm_layer(2, 8, 24, 9.0, mlp=None), mlstm_layer(3, 16, 8, 20.0, mlp=dense(56))],
+}
+CONFIG_L = {
+    "architecture": "Fofinex", "vocab": 72, "width": 64, "norm": {"eps": 1e-6},
+    "layers": [latent_layer(4, 8, 8, 16, 32, 24, 0.5, base=300.0, mlp=moe(4, 2, 24, groups=(2, 1), scale=1.2, shared=16)),
+               latent_layer(2, 16, 16, 8, 16, 48, 0.45, base=1e6, scaling=(32.0, 16, 2.0, 1.0), mlp=None)],
+}
+CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "Bd": without_experts(CONFIG_B), "Cd": without_experts(CONFIG_C),
+           "W": CONFIG_W, "M": CONFIG_M, "L": CONFIG_L}
 
 
 def make_weights(cfg: dict, seed: int) -> dict[str, np.ndarray]:
@@ -148,7 +168,7 @@ def write_folder(folder, cfg: dict, weights: dict, dtype: str):
 
 def make_folder(tmp_path, which: str, dtype: str, seed: int = 0):
     cfg = CONFIGS[which]
-    return write_folder(tmp_path / f"fofinex_{which}_{dtype}", cfg, make_weights(cfg, seed + "ABC".index(which[0])), dtype), cfg
+    return write_folder(tmp_path / f"fofinex_{which}_{dtype}", cfg, make_weights(cfg, seed + "ABCWML".index(which[0])), dtype), cfg
 
 
 def load_plain(folder):

@@ -45,15 +45,21 @@ def assert_close(got, ref, dtype, what="", cfg=None):
     fofinex_util.assert_close(got, ref, dtype, what, routed=cfg is None or is_routed(cfg))
 
 
+# other makes of model: whole prompts and single tokens only
+OTHER_CASES = [(which, dtype) for which in ("W", "M", "L") for dtype in ("float32", "bfloat16")]
+
+
 def all_places(n):
     return list(range(n))
 
 
-@pytest.mark.parametrize("which,dtype", CASES)
+@pytest.mark.parametrize("which,dtype", CASES + OTHER_CASES)
 def test_whole_prompts(models, which, dtype):
     key, pcfg, w, model = models(which, dtype)
     engine = qs.Engine(model, max_tokens=512, max_batch=2)
-    rng = np.random.default_rng(1)
+    # An empty memory's first output is v times the sign of k.q (the quotient's denominator is |n.q| = b |k.q|): a token
+    # whose k.q lies within bfloat16's rounding of zero tests no kernel, and the memories-only model met one.
+    rng = np.random.default_rng(21 if which == "M" else 1)
     for n in (1, 2, 33, 64, 65, 389):       # from 256 tokens on the matrix memory cuts the prompt into chunks
         toks = random_tokens(rng, n, pcfg["vocab"])
         slot = engine.acquire()
@@ -64,7 +70,7 @@ def test_whole_prompts(models, which, dtype):
     engine.cache.check()
 
 
-@pytest.mark.parametrize("which,dtype", CASES)
+@pytest.mark.parametrize("which,dtype", CASES + OTHER_CASES)
 @pytest.mark.parametrize("graphs", [True, False])
 def test_token_by_token_equals_the_prompt(models, which, dtype, graphs):
     """The first tokens of a sequence one by one from an empty state, then on across a page border."""
