@@ -114,7 +114,7 @@ __global__ void moe_expert_up_kernel(T* __restrict__ hidden, size_t ldh, const T
     const T* w = w_up + (size_t)idx[pair] * F * D;
     for (int f = f0 + warp; f < min(F, f0 + rows_per_block); f += warps) {
         const float acc = warp_dot(w + (size_t)f * D, xs, D, lane, vec != 0);
-        if (lane == 0) hidden[(size_t)pair * ldh + f] = from_f32<T>(apply_activation(acc, act));
+        if (lane == 0) hidden[(size_t)pair * ldh + f] = from_f32<T>(apply_activation_wide(acc, act));
     }
 }
 

@@ -322,6 +322,9 @@ int launch_scan(int mode, int phase, float* o, long long ldo, const void* q, lon
     const int KS = 1 << ks_log2;
     int cols = CPT * 256 / KS;
     if (cols > dv) cols = (dv + CPT - 1) / CPT * CPT;
+    // the blocks of a head share its columns evenly: a count just above a block's width (a column more, as the gated
+    // form has) would else leave a second block with a column or two and the whole staging to do for them
+    { const int nb = (dv + cols - 1) / cols; cols = ((dv + nb - 1) / nb + CPT - 1) / CPT * CPT; }
     // few sequences and heads: narrower blocks, so that more SMs take part
     while (cols > 8 * CPT && (long long)n_seq * H * ((dv + cols - 1) / cols) < 148 && cols / CPT * KS > 64)
         cols = (cols / 2 + CPT - 1) / CPT * CPT;       // whole pairs of columns, also for an odd count

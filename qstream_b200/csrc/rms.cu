@@ -212,7 +212,7 @@ __global__ void activate_kernel(T* __restrict__ x, size_t ld, int n, int act) {
     grid_dep_launch();
     grid_dep_wait();
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
-    if (c < n) x[(size_t)blockIdx.x * ld + c] = from_f32<T>(apply_activation(to_f32(x[(size_t)blockIdx.x * ld + c]), act));
+    if (c < n) x[(size_t)blockIdx.x * ld + c] = from_f32<T>(apply_activation_wide(to_f32(x[(size_t)blockIdx.x * ld + c]), act));
 }
 
 // ----------------------------------------------------------------------------- hashed-pair embedding

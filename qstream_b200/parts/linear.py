@@ -12,6 +12,7 @@ import torch
 from ..csrc import ops
 
 TENSOR_CORE_ACTIVATIONS = (None, "none", "gelu_new", "gelu")
+OWN_KERNEL_ACTIVATIONS = ("relu2",)         # in no product's epilogue: applied by a kernel of their own behind the product
 
 
 def linear(x, weight, bias=None, activation=None, residuals=(), out_dtype=None, out=None) -> torch.Tensor:
@@ -24,6 +25,8 @@ def linear(x, weight, bias=None, activation=None, residuals=(), out_dtype=None, 
                 return gemm_tc.linear(x, weight, bias, activation, residuals, out_dtype, out)
             if not residuals:       # an activation that the tensor-core epilogue does not offer: a kernel of its own behind it
                 return ops.activate(gemm_tc.linear(x, weight, bias, None, (), out_dtype, out), activation)
+    if activation in OWN_KERNEL_ACTIVATIONS and not residuals:
+        return ops.activate(ops.linear_simt(x, weight, bias, None, (), out_dtype, out), activation)
     return ops.linear_simt(x, weight, bias, activation, residuals, out_dtype, out)
 
 

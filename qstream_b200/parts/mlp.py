@@ -130,11 +130,9 @@ class RoutedExperts(FeedForward):
             y = torch.empty((rows.shape[0], s.width), dtype=torch.float32, device=h.device)
             bounds = offsets.tolist()                   # waits for the device: how many rows each expert got
             ranges = [(e, bounds[e], bounds[e + 1]) for e in range(s.n_experts) if bounds[e + 1] > bounds[e]]
-            fused = h.dtype != torch.bfloat16           # the CUDA-core product has the activation in its epilogue
             for e, lo, hi in ranges:
-                linear(rows[lo:hi], self.w_up[e], activation=s.activation if fused else None, out=hidden[lo:hi])
-            if not fused:
-                ops.activate(hidden, s.activation)      # one launch for all experts' rows
+                linear(rows[lo:hi], self.w_up[e], out=hidden[lo:hi])
+            ops.activate(hidden, s.activation)          # one launch for all experts' rows
             for e, lo, hi in ranges:
                 linear(hidden[lo:hi], self.w_down[e], out=y[lo:hi])
             out = ops.moe_combine(y, pair_place, wts, b.tok_slot, shared, gate)
