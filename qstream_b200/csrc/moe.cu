@@ -285,3 +285,117 @@ QS_API int qs_moe_combine(float* out, long long ldo, const void* y, int y_dtype,
     if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "moe_combine: %s", cudaGetErrorString(e));
     return qs_check_launch("moe_combine");
 }
+
+// The matrix products of the library (csrc/gemm_tc.cu, csrc/linear_simt.cu).
+extern "C" int qs_gemm_tc(void* C, int c_dtype, const void* A, const void* W, const void* bias, int bias_dtype, int act,
+                          const void* res1, const void* res2, int M, int N, int K, long long lda, long long ldw,
+                          long long ldc, long long ldr, float* ws, long long ws_floats, int32_t* counters, int n_counters,
+                          int32_t* status, int smem_kb, cudaStream_t stream);
+extern "C" int qs_linear_simt(void* C, int c_dtype, const void* A, int a_dtype, const void* W, int w_dtype,
+                              const void* bias, int bias_dtype, int act, const void* res1, const void* res2,
+                              int M, int N, int K, long long lda, long long ldc, long long ldr, cudaStream_t stream);
+
+// One product per expert over its rows, all launched by this one call: C[rows of e] = A[rows of e] W[e]^T with
+// W [E][N][K] and the experts' row ranges `offsets` (E + 1 entries, on the HOST).  `use_tc`: the tensor-core product
+// (bfloat16 operands that it takes) with its scratch `ws`, `counters`, `status`; else the CUDA-core product.
+//
+// An expert's product is small (a thousand rows fill a sixth of the SMs with tiles), so the experts are dealt to
+// EXPERT_STREAMS streams of the library's own that fork from `stream` and join it again before the call returns; each
+// stream has its own share of the scratch.  While `stream` is being captured everything stays on it, in order.
+namespace {
+constexpr int EXPERT_STREAMS = 8, MAX_DEVICES = 16;
+struct ExpertStreams { cudaStream_t side[EXPERT_STREAMS]; cudaEvent_t fork, join[EXPERT_STREAMS]; bool ready; };
+ExpertStreams g_expert_streams[MAX_DEVICES];
+
+ExpertStreams* expert_streams() {
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= MAX_DEVICES) return nullptr;
+    ExpertStreams& p = g_expert_streams[device];
+    if (!p.ready) {
+        if (cudaEventCreateWithFlags(&p.fork, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+        for (int i = 0; i < EXPERT_STREAMS; ++i)
+            if (cudaStreamCreateWithFlags(&p.side[i], cudaStreamNonBlocking) != cudaSuccess ||
+                cudaEventCreateWithFlags(&p.join[i], cudaEventDisableTiming) != cudaSuccess) return nullptr;
+        p.ready = true;
+    }
+    return &p;
+}
+}  // namespace
+
+QS_API int qs_expert_products(void* C, int c_dtype, long long ldc, const void* A, int a_dtype, long long lda, const void* W,
+                              int w_dtype, const int32_t* offsets, int E, int N, int K, int use_tc, float* ws,
+                              long long ws_floats, int32_t* counters, int n_counters, int32_t* status, cudaStream_t stream) {
+    QS_REQUIRE(E > 0 && N > 0 && K > 0 && offsets, "expert_products: bad sizes");
+    const size_t a_size = a_dtype == QS_F32 ? 4 : 2, c_size = c_dtype == QS_F32 ? 4 : 2, w_size = w_dtype == QS_F32 ? 4 : 2;
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    ExpertStreams* pool = nullptr;
+    if (E > 1 && cudaStreamIsCapturing(stream, &capturing) == cudaSuccess && capturing == cudaStreamCaptureStatusNone)
+        pool = expert_streams();
+    const int lanes = pool ? EXPERT_STREAMS : 1;
+    const long long ws_share = ws_floats / lanes / 4 * 4;
+    const int counter_share = n_counters / lanes;
+    if (pool) {
+        if (cudaEventRecord(pool->fork, stream) != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "expert_products: cannot fork");
+        for (int i = 0; i < lanes; ++i) cudaStreamWaitEvent(pool->side[i], pool->fork, 0);
+    }
+    int rc = QS_OK;
+    for (int e = 0; e < E && rc == QS_OK; ++e) {
+        const int lo = offsets[e], M = offsets[e + 1] - lo;
+        if (M <= 0) continue;
+        const int lane = e % lanes;
+        cudaStream_t st = pool ? pool->side[lane] : stream;
+        char* c = (char*)C + (size_t)lo * ldc * c_size;
+        const char* a = (const char*)A + (size_t)lo * lda * a_size;
+        const char* w = (const char*)W + (size_t)e * N * K * w_size;
+        rc = use_tc ? qs_gemm_tc(c, c_dtype, a, w, nullptr, 0, QS_ACT_NONE, nullptr, nullptr, M, N, K, lda, K, ldc, N,
+                                 ws + (size_t)lane * ws_share, ws_share, counters + (size_t)lane * counter_share, counter_share,
+                                 status, 0, st)
+                    : qs_linear_simt(c, c_dtype, a, a_dtype, w, w_dtype, nullptr, 0, QS_ACT_NONE, nullptr, nullptr, M, N, K, lda,
+                                     ldc, N, st);
+    }
+    if (pool)                                           // also after a failed launch: `stream` must not run ahead of the others
+        for (int i = 0; i < lanes; ++i) {
+            cudaEventRecord(pool->join[i], pool->side[i]);
+            cudaStreamWaitEvent(stream, pool->join[i], 0);
+        }
+    return rc;
+}
+
+// One product per head over the same rows, dealt to the same streams: C[:, head h] = A[:, head h] W[h]^T with W [H][N][K],
+// head h's K inputs at A + h * head_a and its N results at C + h * head_c (elements), rows `lda` and `ldc` apart.
+QS_API int qs_head_products(void* C, int c_dtype, long long ldc, long long head_c, const void* A, int a_dtype, long long lda,
+                            long long head_a, const void* W, int w_dtype, int M, int H, int N, int K, int use_tc, float* ws,
+                            long long ws_floats, int32_t* counters, int n_counters, int32_t* status, cudaStream_t stream) {
+    QS_REQUIRE(M > 0 && H > 0 && N > 0 && K > 0, "head_products: bad sizes");
+    const size_t a_size = a_dtype == QS_F32 ? 4 : 2, c_size = c_dtype == QS_F32 ? 4 : 2, w_size = w_dtype == QS_F32 ? 4 : 2;
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    ExpertStreams* pool = nullptr;
+    if (H > 1 && cudaStreamIsCapturing(stream, &capturing) == cudaSuccess && capturing == cudaStreamCaptureStatusNone)
+        pool = expert_streams();
+    const int lanes = pool ? EXPERT_STREAMS : 1;
+    const long long ws_share = ws_floats / lanes / 4 * 4;
+    const int counter_share = n_counters / lanes;
+    if (pool) {
+        if (cudaEventRecord(pool->fork, stream) != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "head_products: cannot fork");
+        for (int i = 0; i < lanes; ++i) cudaStreamWaitEvent(pool->side[i], pool->fork, 0);
+    }
+    int rc = QS_OK;
+    for (int h = 0; h < H && rc == QS_OK; ++h) {
+        const int lane = h % lanes;
+        cudaStream_t st = pool ? pool->side[lane] : stream;
+        char* c = (char*)C + (size_t)h * head_c * c_size;
+        const char* a = (const char*)A + (size_t)h * head_a * a_size;
+        const char* w = (const char*)W + (size_t)h * N * K * w_size;
+        rc = use_tc ? qs_gemm_tc(c, c_dtype, a, w, nullptr, 0, QS_ACT_NONE, nullptr, nullptr, M, N, K, lda, K, ldc, N,
+                                 ws + (size_t)lane * ws_share, ws_share, counters + (size_t)lane * counter_share, counter_share,
+                                 status, 0, st)
+                    : qs_linear_simt(c, c_dtype, a, a_dtype, w, w_dtype, nullptr, 0, QS_ACT_NONE, nullptr, nullptr, M, N, K, lda,
+                                     ldc, N, st);
+    }
+    if (pool)
+        for (int i = 0; i < lanes; ++i) {
+            cudaEventRecord(pool->join[i], pool->side[i]);
+            cudaStreamWaitEvent(stream, pool->join[i], 0);
+        }
+    return rc;
+}

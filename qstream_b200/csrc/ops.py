@@ -512,6 +512,26 @@ def head_linear(out, x, w, n_heads: int) -> None:
                                    dtype_code(x), T, H, N, K, stream()))
 
 
+def head_products(out, x, w, n_heads: int) -> None:
+    """The same as `head_linear` for steps of many tokens: one matrix product per head (tensor cores where the
+    operands allow), all launched by one call and dealt to several streams."""
+    from . import gemm_tc
+    H, N, K = w.shape
+    T = x.shape[0]
+    if H != n_heads or x.shape[1] % H or out.shape[1] % H or w.dtype != x.dtype or out.dtype != x.dtype or not w.is_contiguous():
+        raise QStreamError(QsError.INVALID_INPUT, "head_products: operands do not fit")
+    head_x, head_o = x.shape[1] // H, out.shape[1] // H
+    use_tc = gemm_tc.takes(x[:, :K], w[0]) and head_x % 8 == 0
+    ws, counters = gemm_tc.scratch(x.device) if use_tc else (None, None)
+    rc = bind("qs_head_products", [c_void_p, c_int, c_longlong, c_longlong, c_void_p, c_int, c_longlong, c_longlong, c_void_p, c_int,
+                                    c_int, c_int, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p])(
+        ptr(out), dtype_code(out), out.stride(0), head_o, ptr(x), dtype_code(x), x.stride(0), head_x, ptr(w), dtype_code(w),
+        T, H, N, K, int(use_tc), ptr(ws), ws.numel() if use_tc else 0, ptr(counters), counters.numel() if use_tc else 0,
+        ptr(gemm_tc.status_word(x.device)) if use_tc else None, stream())
+    count_launches(H - 1)
+    check(rc)
+
+
 # ------------------------------------------------------------------------------- routed experts
 
 def moe_route(z, correction, n_experts, top, groups, keep, scale, gate_col=-1):
@@ -555,6 +575,27 @@ def moe_sort(idx, n_experts: int):
     check(library().qs_moe_sort(ptr(offsets), ptr(place_token), ptr(pair_place), _int32(idx, "idx"), T * top, top,
                                 int(n_experts), stream()))
     return offsets, place_token, pair_place
+
+
+def expert_products(out, x, w_all, offsets) -> None:
+    """out[rows of e] = x[rows of e] @ w_all[e].T for every expert e, rows offsets[e] .. offsets[e + 1] (a list on the
+    host); w_all is [experts, N, K].  One call launches all the products."""
+    import numpy as np
+    from . import gemm_tc
+    E, N, K = w_all.shape
+    rows, K2, lda = _rows(x)
+    if K2 != K or out.shape != (rows, N) or out.stride(1) != 1 or not w_all.is_contiguous() or len(offsets) != E + 1:
+        raise QStreamError(QsError.INVALID_INPUT, "expert_products: operands do not fit")
+    bounds = np.ascontiguousarray(offsets, dtype=np.int32)
+    use_tc = gemm_tc.takes(x, w_all[0])
+    ws, counters = gemm_tc.scratch(x.device) if use_tc else (None, None)
+    rc = bind("qs_expert_products", [c_void_p, c_int, c_longlong, c_void_p, c_int, c_longlong, c_void_p, c_int, c_void_p, c_int,
+                                      c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p])(
+        ptr(out), dtype_code(out), out.stride(0), ptr(x), dtype_code(x), lda, ptr(w_all), dtype_code(w_all),
+        bounds.ctypes.data, E, N, K, int(use_tc), ptr(ws), ws.numel() if use_tc else 0, ptr(counters),
+        counters.numel() if use_tc else 0, ptr(gemm_tc.status_word(x.device)) if use_tc else None, stream())
+    count_launches(sum(1 for e in range(E) if offsets[e + 1] > offsets[e]) - 1)
+    check(rc)
 
 
 def moe_combine(y, pair_place, wts, tok_slot, add=None, add_scale=None) -> torch.Tensor:

@@ -347,15 +347,9 @@ def kernel_table_fofinex(torch, np, pk, width=2048, T=4096, batch=32, ctx=2048):
         yy = torch.empty((rows_.shape[0], width), dtype=torch.float32, device=dev)
         hid = torch.empty((rows_.shape[0], F), dtype=bf, device=dev)
         bounds = offsets.tolist()
-        for e in range(E):
-            lo, hi = bounds[e], bounds[e + 1]
-            if hi > lo:
-                linear(rows_[lo:hi], w_up[e], out=hid[lo:hi])
+        ops.expert_products(hid, rows_, w_up, bounds)
         ops.activate(hid, "relu2")
-        for e in range(E):
-            lo, hi = bounds[e], bounds[e + 1]
-            if hi > lo:
-                linear(hid[lo:hi], w_down[e], out=yy[lo:hi])
+        ops.expert_products(yy, hid, w_down, bounds)
         return ops.moe_combine(yy, pair_place, wts, slot_all)
     add(f"experts ordered by expert, {T} tokens (sort, gather, {2 * E} products, activation, combine)", "feed-forward products",
         t.kernel(grouped, repeats=5), flops=4.0 * T * top * F * width, bound="tensor")

@@ -85,19 +85,11 @@ class LatentAttention(Mixer):
         T = q.shape[0]
         q_abs = torch.empty((T, H * (r + dr)), dtype=q.dtype, device=q.device)
         ops.latent_q_rotate(q_abs, q, H, dn, dr, r, pos.rotary_dim, pos.frequencies, pos.magnitude, b.tok_slot, b.tok_pos)
-        few = T <= FEW_TOKENS                   # one launch for all heads; else a tensor-core product per head
-        if few:
-            ops.head_linear(q_abs, q, self.w_uk_t, H)
-        else:
-            for i in range(H):
-                linear(q[:, i * (dn + dr):i * (dn + dr) + dn], self.w_uk_t[i], out=q_abs[:, i * (r + dr):i * (r + dr) + r])
+        few = T <= FEW_TOKENS                   # one launch for all heads; else a product per head, dealt to several streams
+        (ops.head_linear if few else ops.head_products)(q_abs, q, self.w_uk_t, H)
         latent = attend(q_abs, self.as_attention, step, view)
         o = torch.empty((T, H * dv), dtype=q.dtype, device=q.device)
-        if few:
-            ops.head_linear(o, latent, self.w_uv_heads, H)
-        else:
-            for i in range(H):
-                linear(latent[:, i * r:(i + 1) * r], self.w_uv[i * dv:(i + 1) * dv], out=o[:, i * dv:(i + 1) * dv])
+        (ops.head_linear if few else ops.head_products)(o, latent, self.w_uv_heads, H)
         return linear(o, self.w_out, None, residuals=residuals, out_dtype=out_dtype)
 
 

@@ -129,12 +129,9 @@ class RoutedExperts(FeedForward):
             hidden = torch.empty((rows.shape[0], s.inner), dtype=h.dtype, device=h.device)
             y = torch.empty((rows.shape[0], s.width), dtype=torch.float32, device=h.device)
             bounds = offsets.tolist()                   # waits for the device: how many rows each expert got
-            ranges = [(e, bounds[e], bounds[e + 1]) for e in range(s.n_experts) if bounds[e + 1] > bounds[e]]
-            for e, lo, hi in ranges:
-                linear(rows[lo:hi], self.w_up[e], out=hidden[lo:hi])
-            ops.activate(hidden, s.activation)          # one launch for all experts' rows
-            for e, lo, hi in ranges:
-                linear(hidden[lo:hi], self.w_down[e], out=y[lo:hi])
+            ops.expert_products(hidden, rows, self.w_up, bounds)        # a product per expert, launched by one call
+            ops.activate(hidden, s.activation)                          # one launch for all experts' rows
+            ops.expert_products(y, hidden, self.w_down, bounds)
             out = ops.moe_combine(y, pair_place, wts, b.tok_slot, shared, gate)
         if residuals:
             raise QStreamError(QsError.INVALID_INPUT, "routed experts: residuals are added by the arrangement")
